@@ -9,7 +9,7 @@
  *
  * All file:line citations are relative to /root/reference.  The reference's Release build (g++ 13.3,
  * -O3 -mavx2 -mfma) decides where `s += a*b` becomes one FMA and where it stays two roundings; those
- * decisions were read off the disassembly of oracle/_ref and are written out explicitly here (fmaf()
+ * decisions are written out explicitly here (fmaf()
  * = fused, `p = a*b; s = s + p` = un-fused), and this file is compiled with -ffp-contract=off so the
  * rounding does not depend on compiler flags.
  */
@@ -89,7 +89,7 @@ void tio_dequantize_int4(const int32_t* q, float* x, size_t n, float scale, floa
 /* matmul_2d, :538-592 (and matmul_3d_2d :594-640, same inner loops).
  *
  * What the reference COMPUTES per output element is pinned by its Release build (g++ 13.3, -O3 -mavx2
- * -mfma), observed in the disassembly of oracle/_ref and verified bit-for-bit by tests/test_oracle_vs_ref.py:
+ * -mfma) and verified bit-for-bit by tests/test_oracle_vs_ref.py:
  *
  *  - scalar i-j-k loop (:565-573, :625-633; taken when M < 32 or N < 32 or K < 32, i.e. every decode GEMV):
  *    GCC vectorises the k loop 4-wide as an IN-ORDER reduction: the four products are rounded on their
