@@ -39,6 +39,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+# The layered sequence engine (include/ti_b200_seq.h) is a library of its own: a model that only needs it does not wait for the
+# quantized-decoder library to compile.
+SEQ_LIB = os.path.join(HERE, "libturboinfer_b200_seq.so")
+SEQ_SOURCES = ["seq_engine.cu"]
+SEQ_HEADERS = ["seq_kernels.cuh", "sampling.cuh", "kernels.cuh", "gemv.cuh", "qlayout.cuh", "ptx.cuh"]
+
+
+def build_seq(force: bool = False) -> str:
+    deps = [os.path.join(CSRC, f) for f in SEQ_SOURCES + SEQ_HEADERS] + [os.path.join(HERE, "..", "include", "ti_b200_seq.h")]
+    if not force and os.path.exists(SEQ_LIB) and all(os.path.getmtime(d) <= os.path.getmtime(SEQ_LIB) for d in deps):
+        return SEQ_LIB
+    tmp = SEQ_LIB + ".%d.tmp" % os.getpid()
+    cmd = [NVCC, *FLAGS, "-o", tmp, *[os.path.join(CSRC, s) for s in SEQ_SOURCES], "-lcudart"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    try:
+        with open(os.path.join(HERE, "build_seq.log"), "w") as f:
+            f.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
+    except OSError:
+        pass
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building libturboinfer_b200_seq.so")
+    os.replace(tmp, SEQ_LIB)
+    return SEQ_LIB
+
+
 HOST_LIB = os.path.join(HERE, "libturboinfer_b200_host.so")
 HOST_SRC = os.path.join(HERE, "host", "turboinfer_host.cpp")
 CXX = os.environ.get("TI_HOST_CXX", "/usr/bin/g++")
@@ -76,4 +102,5 @@ def build_host_test(out_path: str) -> str:
 
 if __name__ == "__main__":
     build(force=True, verbose=True)
+    build_seq(force=True)
     build_host(force=True)

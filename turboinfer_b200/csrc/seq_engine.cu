@@ -1,0 +1,1009 @@
+// seq_engine.cu -- implementation of include/ti_b200_seq.h: the layered sequence engine (sm_100a).
+//
+// Host side: model description and named tensors, the page pool / state-slot manager, the ragged step, the
+// continuous-batching generation loop and the sampler launch.  Device side: seq_kernels.cuh (+ sampling.cuh, the sampler the
+// rest of the library uses).  One library stream; a step is enqueued without host synchronisation until its results are read.
+#include "../../include/ti_b200_seq.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "seq_kernels.cuh"
+#include "sampling.cuh"
+
+using namespace tib;
+using namespace tib::seq;
+
+namespace {
+
+thread_local std::string g_err;
+int g_device = -1, g_num_sms = 0;
+cudaStream_t g_stream = nullptr;
+uint64_t g_launches = 0;
+size_t g_smem_optin = 0;
+
+int fail(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return 1;
+}
+#define CK(call)                                                                                   \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess) return fail("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+#define TRY(expr)            \
+    do {                     \
+        int rc_ = (expr);    \
+        if (rc_ != 0) return rc_; \
+    } while (0)
+#define LAUNCHED()     \
+    do {               \
+        ++g_launches;  \
+        CK(cudaGetLastError()); \
+    } while (0)
+
+template <typename T>
+struct DevBuf {
+    T* p = nullptr;
+    size_t n = 0;
+    DevBuf() = default;
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+    DevBuf(DevBuf&& o) noexcept : p(o.p), n(o.n) { o.p = nullptr; o.n = 0; }
+    DevBuf& operator=(DevBuf&& o) noexcept {
+        if (this != &o) { release(); p = o.p; n = o.n; o.p = nullptr; o.n = 0; }
+        return *this;
+    }
+    ~DevBuf() { release(); }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        n = 0;
+    }
+    int alloc(size_t count) {
+        release();
+        if (count == 0) return 0;
+        cudaError_t e = cudaMalloc(&p, count * sizeof(T));
+        if (e != cudaSuccess) return fail("cudaMalloc(%zu bytes) failed: %s", count * sizeof(T), cudaGetErrorString(e));
+        n = count;
+        return 0;
+    }
+    int ensure(size_t count) { return count <= n ? 0 : alloc(count); }
+};
+
+int grid_for(size_t n, int block = 256) {
+    size_t g = (n + block - 1) / block;
+    return (int)std::max<size_t>(1, std::min(g, (size_t)g_num_sms * 8));
+}
+
+// ---- tensors ---------------------------------------------------------------------------------------------------------
+// a matrix is kept in the model's weight type (bf16 or fp32), everything else (gains, mixing vectors, decay offsets) in fp32
+struct Tensor {
+    std::vector<int64_t> shape;
+    bool matrix = false;
+    bool set = false;
+    DevBuf<uint8_t> data;
+    size_t count() const {
+        size_t c = 1;
+        for (auto s : shape) c *= (size_t)s;
+        return c;
+    }
+};
+
+__global__ void synth_fill_f32_kernel(float* out, size_t n, uint64_t seed, float amp, float offset) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = synth_uniform(seed, i, amp) + offset;
+}
+// first maximum of every row (temperature 0); its log-probability under softmax(logits) when asked for
+__global__ void argmax_rows_kernel(const float* logits, int V, int ld, int* tok, float* logprob) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    __shared__ float red[32];
+    const float* r = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int idx = 0x7FFFFFFF;
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+        if (r[i] > best) { best = r[i]; idx = i; }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
+        if (ob > best || (ob == best && oi < idx)) { best = ob; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    best = bv[0];
+    idx = bi[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+        if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+    float s = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) s += expf(r[i] - best);
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) {
+        tok[blockIdx.x] = idx == 0x7FFFFFFF ? 0 : idx;
+        if (logprob) logprob[blockIdx.x] = -logf(s);
+    }
+}
+
+struct LayerW {
+    ti_seq_layer_desc d{};
+    // attention: fused [q | k | v | gate] rows, output projection, frequencies
+    const void *qkvg = nullptr, *o = nullptr;
+    int n_qkvg = 0;
+    DevBuf<uint8_t> qkvg_buf;
+    DevBuf<float> inv_freq;
+    // wkv
+    const void *r = nullptr, *k = nullptr, *v = nullptr, *g = nullptr, *w1 = nullptr, *w2 = nullptr;
+    DevBuf<float> mu;   // [5][D]: r, k, v, g, w
+    const float *w0 = nullptr, *u = nullptr, *normw = nullptr;
+    // feed-forward: fused [gate | up] rows, down
+    const void *gateup = nullptr, *down = nullptr;
+    DevBuf<uint8_t> gateup_buf;
+    const float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr;
+};
+
+// one execution of a layer: a looped layer runs several times, every run with its own cache or state
+struct Run {
+    int layer = 0;
+    bool enters_pass = false;   // the looped block's input projection comes right before this run
+    DevBuf<float> k_pool, v_pool;          // attention: [pages * 64][G * d], [pages * 64][G * dv]
+    DevBuf<float> state, prev;             // wkv: [slots][H][d][d], [slots][D]
+};
+
+struct SeqState {
+    bool live = false;
+    int len = 0;
+    std::vector<int> pages;
+};
+
+struct Model {
+    ti_seq_model_desc d{};
+    std::vector<LayerW> layers;
+    std::vector<Run> runs;
+    std::map<std::string, Tensor> tensors;
+    std::vector<std::string> order;   // required tensors in a fixed order
+    bool finalized = false;
+    size_t wsize = 2;                 // bytes per matrix element
+    const void *embed = nullptr, *loop_in = nullptr, *head = nullptr;
+    const float* final_norm = nullptr;
+    // cache manager
+    int num_pages = 0;
+    std::vector<int> free_pages;
+    std::vector<SeqState> seqs;
+    // step scratch
+    int cap_rows = 0, cap_want = 0;
+    DevBuf<float> x, x0, xc, h, proj, mixes, att, mo, act, lora, hn, logits, logprobs;
+    DevBuf<int> meta, picks;
+    int* meta_host = nullptr;
+    size_t meta_host_cap = 0;
+    int max_proj = 0, max_att = 0, max_ff = 0, max_rank = 0;
+    bool any_wkv = false;
+    // debug
+    bool dbg = false;
+    DevBuf<float> dbg_buf;
+    int dbg_rows = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+    ~Model() {
+        if (meta_host) cudaFreeHost(meta_host);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+    }
+};
+
+std::mutex g_mu;
+std::vector<std::unique_ptr<Model>> g_models;
+Model* get_model(ti_seq_model_t h) {
+    if (h == 0 || h > g_models.size()) return nullptr;
+    return g_models[h - 1].get();
+}
+
+void require(Model& m, const std::string& name, std::vector<int64_t> shape, bool matrix) {
+    Tensor t;
+    t.shape = std::move(shape);
+    t.matrix = matrix;
+    m.tensors[name] = std::move(t);
+    m.order.push_back(name);
+}
+
+int describe_tensors(Model& m) {
+    const int64_t D = m.d.width, V = m.d.vocab;
+    require(m, "embed", {V, D}, true);
+    if (m.d.loop_times > 0) require(m, "loop.in", {D, 2 * D}, true);
+    for (int i = 0; i < m.d.n_layers; ++i) {
+        const ti_seq_layer_desc& L = m.layers[i].d;
+        const std::string p = "l" + std::to_string(i) + ".";
+        require(m, p + "norm1", {}, false);
+        require(m, p + "norm1b", {}, false);
+        if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
+            if (L.heads <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) return fail("layer %d: heads %d / kv_heads %d", i, L.heads, L.kv_heads);
+            if (L.dim <= 0 || L.vdim <= 0 || L.dim > 32 * kAttnMaxPerLane || L.vdim > 32 * kAttnMaxPerLane)
+                return fail("layer %d: head sizes %d / %d outside 1..%d", i, L.dim, L.vdim, 32 * kAttnMaxPerLane);
+            if (L.rot_dims < 0 || L.rot_dims > L.dim || (L.rot_dims & 1)) return fail("layer %d: rot dims %d of %d", i, L.rot_dims, L.dim);
+            require(m, p + "mix.q", {(int64_t)L.heads * L.dim, D}, true);
+            require(m, p + "mix.k", {(int64_t)L.kv_heads * L.dim, D}, true);
+            require(m, p + "mix.v", {(int64_t)L.kv_heads * L.vdim, D}, true);
+            if (L.out_gate) require(m, p + "mix.g", {(int64_t)L.heads, D}, true);
+            require(m, p + "mix.o", {D, (int64_t)L.heads * L.vdim}, true);
+        } else if (L.mixer == TI_SEQ_MIXER_WKV) {
+            if (L.heads <= 0 || L.dim <= 0 || L.dim > 1024 || L.decay_rank <= 0) return fail("layer %d: wkv heads %d dim %d rank %d", i, L.heads, L.dim, L.decay_rank);
+            const int64_t C = (int64_t)L.heads * L.dim;
+            for (const char* s : {"r", "k", "v", "g", "w"}) require(m, p + "mix.mu." + s, {D}, false);
+            for (const char* s : {"r", "k", "v", "g"}) require(m, p + "mix." + s, {C, D}, true);
+            require(m, p + "mix.w1", {(int64_t)L.decay_rank, D}, true);
+            require(m, p + "mix.w2", {C, (int64_t)L.decay_rank}, true);
+            require(m, p + "mix.w0", {C}, false);
+            require(m, p + "mix.u", {(int64_t)L.heads, (int64_t)L.dim}, false);
+            require(m, p + "mix.norm", {C}, false);
+            require(m, p + "mix.o", {D, C}, true);
+        } else {
+            return fail("layer %d: unknown mixer %d", i, L.mixer);
+        }
+        if (L.ff > 0) {
+            require(m, p + "norm2", {}, false);
+            require(m, p + "norm2b", {}, false);
+            require(m, p + "mlp.gate", {(int64_t)L.ff, D}, true);
+            require(m, p + "mlp.up", {(int64_t)L.ff, D}, true);
+            require(m, p + "mlp.down", {D, (int64_t)L.ff}, true);
+        }
+    }
+    require(m, "final.norm", {}, false);
+    require(m, "head", {V, D}, true);
+    return 0;
+}
+
+// store `n` source elements (fp32 on the device) into the tensor's own format
+int store_from_f32(Model& m, Tensor& t, const float* src_dev, size_t n) {
+    if (t.matrix && m.d.mode == TI_SEQ_BF16) {
+        TRY(t.data.alloc(n * 2));
+        f32_to_bf16_kernel<<<grid_for(n), 256, 0, g_stream>>>(src_dev, reinterpret_cast<__nv_bfloat16*>(t.data.p), n);
+        LAUNCHED();
+    } else {
+        TRY(t.data.alloc(n * 4));
+        CK(cudaMemcpyAsync(t.data.p, src_dev, n * 4, cudaMemcpyDeviceToDevice, g_stream));
+    }
+    CK(cudaStreamSynchronize(g_stream));
+    t.set = true;
+    return 0;
+}
+
+std::vector<float> rotary_frequencies(const ti_seq_layer_desc& L) {
+    std::vector<float> f((size_t)L.rot_dims / 2);
+    const double two_pi = 6.283185307179586476925286766559;
+    for (size_t i = 0; i < f.size(); ++i) {
+        double fi = std::pow((double)L.rot_base, -2.0 * (double)i / (double)L.rot_dims);
+        if (L.rot_scaled) {
+            const double wl = two_pi / fi, orig = L.rot_original;
+            if (wl > orig / L.rot_low) fi = fi / L.rot_factor;
+            else if (!(wl < orig / L.rot_high)) {
+                const double s = (orig / wl - L.rot_low) / ((double)L.rot_high - L.rot_low);
+                fi = (1.0 - s) * fi / L.rot_factor + s * fi;
+            }
+        }
+        f[i] = (float)fi;
+    }
+    return f;
+}
+
+int concat_rows(Model& m, std::initializer_list<const Tensor*> parts, DevBuf<uint8_t>& out, int* rows) {
+    size_t bytes = 0;
+    int n = 0;
+    for (const Tensor* t : parts) {
+        if (!t) continue;
+        bytes += t->data.n;
+        n += (int)t->shape[0];
+    }
+    TRY(out.alloc(bytes));
+    size_t off = 0;
+    for (const Tensor* t : parts) {
+        if (!t) continue;
+        CK(cudaMemcpyAsync(out.p + off, t->data.p, t->data.n, cudaMemcpyDeviceToDevice, g_stream));
+        off += t->data.n;
+    }
+    CK(cudaStreamSynchronize(g_stream));
+    *rows = n;
+    (void)m;
+    return 0;
+}
+
+// ---- matrix product dispatch ----------------------------------------------------------------------------------------------
+int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, int M, int N, int K, int epi = EPI_NONE, float alpha = 1.f) {
+    if (M <= 0 || N <= 0) return 0;
+    const size_t xs_bytes = (size_t)M * K * sizeof(float);
+    if (M <= kGemvMaxRows && xs_bytes <= g_smem_optin) {
+        const int warps = 8;
+        const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * 4));
+        if (m.d.mode == TI_SEQ_BF16)
+            gemv_rows_kernel<__nv_bfloat16><<<grid, warps * 32, xs_bytes, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha);
+        else
+            gemv_rows_kernel<float><<<grid, warps * 32, xs_bytes, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha);
+        LAUNCHED();
+        return 0;
+    }
+    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    if (m.d.mode == TI_SEQ_BF16) gemm_bf16_kernel<<<grid, 128, 0, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha);
+    else gemm_f32_kernel<<<grid, 256, 0, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha);
+    LAUNCHED();
+    return 0;
+}
+
+int ensure_scratch(Model& m, int rows, int want) {
+    if (rows > m.cap_rows) {
+        const size_t R = (size_t)std::max(rows, 64), D = m.d.width;
+        TRY(m.x.alloc(R * D));
+        TRY(m.x0.alloc(R * D));
+        if (m.d.loop_times > 0) TRY(m.xc.alloc(R * 2 * D));
+        TRY(m.h.alloc(R * D));
+        TRY(m.proj.alloc(R * (size_t)m.max_proj));
+        if (m.any_wkv) TRY(m.mixes.alloc(5 * R * D));
+        TRY(m.att.alloc(R * (size_t)m.max_att));
+        TRY(m.mo.alloc(R * D));
+        if (m.max_ff) TRY(m.act.alloc(R * (size_t)m.max_ff));
+        if (m.max_rank) TRY(m.lora.alloc(R * (size_t)m.max_rank));
+        if (m.dbg) TRY(m.dbg_buf.alloc(m.runs.size() * R * D));
+        m.cap_rows = (int)R;
+    }
+    if (want > m.cap_want) {
+        const size_t W = (size_t)std::max(want, 8);
+        TRY(m.hn.alloc(W * m.d.width));
+        TRY(m.logits.alloc(W * m.d.vocab));
+        TRY(m.logprobs.alloc(W));
+        TRY(m.picks.alloc(W));
+        m.cap_want = (int)W;
+    }
+    return 0;
+}
+
+// ---- the step ----------------------------------------------------------------------------------------------------------------
+struct SampleSpec {
+    bool on = false;
+    float temperature = 0.f, top_p = 1.f;
+    int top_k = 0;
+    uint64_t seed = 0;
+    const int32_t* index = nullptr;
+    int32_t* out_tokens = nullptr;
+    float* out_logprobs = nullptr;
+};
+
+int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const int32_t* tokens, int n_want, const int32_t* want_rows,
+             float* logits_host, const SampleSpec& smp) {
+    if (!m.finalized) return fail("model not finalized");
+    if (E <= 0) return 0;
+    const int D = m.d.width, V = m.d.vocab;
+    int T = 0;
+    for (int e = 0; e < E; ++e) {
+        if (seqs[e] < 0 || seqs[e] >= (int)m.seqs.size() || !m.seqs[seqs[e]].live) return fail("step: sequence %d is not open", seqs[e]);
+        for (int f = 0; f < e; ++f)
+            if (seqs[f] == seqs[e]) return fail("step: sequence %d appears twice", seqs[e]);
+        if (counts[e] <= 0) return fail("step: entry %d brings no tokens", e);
+        T += counts[e];
+    }
+    for (int i = 0; i < T; ++i)
+        if (tokens[i] < 0 || tokens[i] >= V) return fail("step: token id %d outside the vocabulary", tokens[i]);
+    for (int i = 0; i < n_want; ++i)
+        if (want_rows[i] < 0 || want_rows[i] >= T) return fail("step: wanted row %d outside the step", want_rows[i]);
+    // pages for the new tokens (all or nothing)
+    int need = 0;
+    for (int e = 0; e < E; ++e) {
+        const SeqState& s = m.seqs[seqs[e]];
+        need += (s.len + counts[e] + kPageTokens - 1) / kPageTokens - (int)s.pages.size();
+    }
+    if (need > (int)m.free_pages.size()) return fail("step: page pool exhausted (%d pages needed, %zu free)", need, m.free_pages.size());
+    for (int e = 0; e < E; ++e) {
+        SeqState& s = m.seqs[seqs[e]];
+        const int np = (s.len + counts[e] + kPageTokens - 1) / kPageTokens;
+        while ((int)s.pages.size() < np) {
+            s.pages.push_back(m.free_pages.back());
+            m.free_pages.pop_back();
+        }
+    }
+    const int n_out = smp.on ? E : n_want;
+    TRY(ensure_scratch(m, T, std::max(n_out, 1)));
+    // meta buffer: tok | row_ent | row_pos | ent_row0 | ent_slot | ent_pos0 | out rows | page table
+    const int stride = m.num_pages;
+    const size_t n_meta = (size_t)3 * T + (size_t)(E + 1) + 2 * (size_t)E + (size_t)std::max(n_out, 1) + (size_t)m.seqs.size() * stride;
+    if (n_meta > m.meta_host_cap) {
+        if (m.meta_host) cudaFreeHost(m.meta_host);
+        m.meta_host = nullptr;
+        m.meta_host_cap = 0;
+        CK(cudaMallocHost(&m.meta_host, n_meta * 2 * sizeof(int)));
+        m.meta_host_cap = n_meta * 2;
+    }
+    TRY(m.meta.ensure(m.meta_host_cap));
+    int* hp = m.meta_host;
+    int *h_tok = hp, *h_ent = h_tok + T, *h_pos = h_ent + T, *h_row0 = h_pos + T, *h_slot = h_row0 + E + 1, *h_pos0 = h_slot + E,
+        *h_out = h_pos0 + E, *h_table = h_out + std::max(n_out, 1);
+    int row = 0;
+    for (int e = 0; e < E; ++e) {
+        const SeqState& s = m.seqs[seqs[e]];
+        h_row0[e] = row;
+        h_slot[e] = seqs[e];
+        h_pos0[e] = s.len;
+        for (int i = 0; i < counts[e]; ++i, ++row) {
+            h_tok[row] = tokens[row];
+            h_ent[row] = e;
+            h_pos[row] = s.len + i;
+        }
+        if (smp.on) h_out[e] = row - 1;
+    }
+    h_row0[E] = row;
+    if (!smp.on)
+        for (int i = 0; i < n_want; ++i) h_out[i] = want_rows[i];
+    for (size_t s = 0; s < m.seqs.size(); ++s)
+        for (int p = 0; p < stride; ++p) h_table[s * stride + p] = p < (int)m.seqs[s].pages.size() ? m.seqs[s].pages[p] : 0;
+    // the previous step's copy out of this pinned buffer has completed: every step ends with a stream synchronisation
+    CK(cudaMemcpyAsync(m.meta.p, hp, n_meta * sizeof(int), cudaMemcpyHostToDevice, g_stream));
+    StepMeta sm{};
+    sm.tok = m.meta.p;
+    sm.row_ent = sm.tok + T;
+    sm.row_pos = sm.row_ent + T;
+    sm.ent_row0 = sm.row_pos + T;
+    sm.ent_slot = sm.ent_row0 + E + 1;
+    sm.ent_pos0 = sm.ent_slot + E;
+    const int* d_out = sm.ent_pos0 + E;
+    sm.page_table = d_out + std::max(n_out, 1);
+    sm.table_stride = stride;
+    sm.T = T;
+    sm.E = E;
+
+    CK(cudaEventRecord(m.ev0, g_stream));
+    const bool bf = m.d.mode == TI_SEQ_BF16;
+    const int nt = 256;
+    if (bf) embed_rows_kernel<__nv_bfloat16><<<T, nt, 0, g_stream>>>((const __nv_bfloat16*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr);
+    else embed_rows_kernel<float><<<T, nt, 0, g_stream>>>((const float*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr);
+    LAUNCHED();
+    const float eps = m.d.norm_eps;
+    for (size_t ri = 0; ri < m.runs.size(); ++ri) {
+        Run& R = m.runs[ri];
+        LayerW& L = m.layers[R.layer];
+        if (R.enters_pass) {
+            concat_rows_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.x0.p, D, m.xc.p);
+            LAUNCHED();
+            TRY(gemm(m, m.xc.p, 2 * D, m.loop_in, m.x.p, D, T, D, 2 * D));
+        }
+        scalar_rmsnorm_kernel<<<T, nt, 0, g_stream>>>(m.x.p, nullptr, D, L.norm1, eps, m.h.p);
+        LAUNCHED();
+        if (L.d.mixer == TI_SEQ_MIXER_ATTENTION) {
+            AttnShape s{};
+            s.heads = L.d.heads; s.kv_heads = L.d.kv_heads; s.dim = L.d.dim; s.vdim = L.d.vdim;
+            s.window = L.d.window; s.rot_dims = L.d.rot_dims; s.qk_norm = L.d.qk_norm; s.out_gate = L.d.out_gate;
+            s.scale = L.d.scale; s.eps = eps; s.ld = L.n_qkvg;
+            TRY(gemm(m, m.h.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
+            attn_prepare_kernel<<<T, 128, 0, g_stream>>>(m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p);
+            LAUNCHED();
+            const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
+            window_attention_kernel<<<dim3(T, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, R.k_pool.p, R.v_pool.p, m.att.p);
+            LAUNCHED();
+            TRY(gemm(m, m.att.p, s.heads * s.vdim, L.o, m.mo.p, D, T, D, s.heads * s.vdim));
+        } else {
+            const int C = L.d.heads * L.d.dim, d = L.d.dim, rank = L.d.decay_rank;
+            wkv_mix_kernel<<<T, nt, 0, g_stream>>>(m.h.p, sm, D, L.mu.p, R.prev.p, m.mixes.p);
+            LAUNCHED();
+            wkv_save_prev_kernel<<<E, nt, 0, g_stream>>>(m.h.p, sm, D, R.prev.p);
+            LAUNCHED();
+            const size_t TD = (size_t)T * D, TC = (size_t)T * C;
+            float *pr = m.proj.p, *pk = pr + TC, *pv = pk + TC, *pg = pv + TC, *pz = pg + TC;
+            TRY(gemm(m, m.mixes.p + 0 * TD, D, L.r, pr, C, T, C, D));
+            TRY(gemm(m, m.mixes.p + 1 * TD, D, L.k, pk, C, T, C, D));
+            TRY(gemm(m, m.mixes.p + 2 * TD, D, L.v, pv, C, T, C, D));
+            TRY(gemm(m, m.mixes.p + 3 * TD, D, L.g, pg, C, T, C, D, EPI_SILU));
+            TRY(gemm(m, m.mixes.p + 4 * TD, D, L.w1, m.lora.p, rank, T, rank, D, EPI_TANH));
+            TRY(gemm(m, m.lora.p, rank, L.w2, pz, C, T, C, rank));
+            WkvArgs a{};
+            a.r = pr; a.k = pk; a.v = pv; a.gate = pg; a.z = pz;
+            a.w0 = L.w0; a.u = L.u; a.normw = L.normw;
+            a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d; a.eps = eps;
+            const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
+            a.s_in_smem = full <= g_smem_optin ? 1 : 0;
+            wkv_scan_kernel<<<dim3(E, L.d.heads), (d + 31) / 32 * 32, a.s_in_smem ? full : small, g_stream>>>(a, sm);
+            LAUNCHED();
+            TRY(gemm(m, m.att.p, C, L.o, m.mo.p, D, T, D, C));
+        }
+        if (L.d.ff > 0) {
+            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm1b, eps, L.norm2, m.h.p);
+            LAUNCHED();
+            const int F = L.d.ff;
+            TRY(gemm(m, m.h.p, D, L.gateup, m.proj.p, 2 * F, T, 2 * F, D));
+            glu_kernel<<<grid_for((size_t)T * F), 256, 0, g_stream>>>(m.proj.p, F, L.d.ff_act, m.act.p, (size_t)T * F);
+            LAUNCHED();
+            TRY(gemm(m, m.act.p, F, L.down, m.mo.p, D, T, D, F));
+            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm2b, eps, nullptr, nullptr);
+            LAUNCHED();
+        } else {
+            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm1b, eps, nullptr, nullptr);
+            LAUNCHED();
+        }
+        if (m.dbg) CK(cudaMemcpyAsync(m.dbg_buf.p + ri * (size_t)T * D, m.x.p, (size_t)T * D * sizeof(float), cudaMemcpyDeviceToDevice, g_stream));
+    }
+    m.dbg_rows = T;
+    if (n_out > 0) {
+        scalar_rmsnorm_kernel<<<n_out, nt, 0, g_stream>>>(m.x.p, d_out, D, m.final_norm, eps, m.hn.p);
+        LAUNCHED();
+        TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale));
+    }
+    if (smp.on) {
+        const bool greedy = !(smp.temperature > 0.f) || smp.top_k == 1;
+        if (greedy) {
+            argmax_rows_kernel<<<E, 256, 0, g_stream>>>(m.logits.p, V, V, m.picks.p, m.logprobs.p);
+            LAUNCHED();
+        } else {
+            const size_t row_smem = sample_row_smem_bytes(V);
+            for (int e = 0; e < E; ++e) {   // one launch per sequence: every sequence has its own RNG stream and counter
+                SampleArgs a{};
+                a.logits = m.logits.p + (size_t)e * V; a.V = V; a.ld = V;
+                a.temperature = smp.temperature; a.top_k = smp.top_k; a.top_p = smp.top_p;
+                a.seed = smp.seed + 0x9E3779B97F4A7C15ull * (uint64_t)(uint32_t)seqs[e];
+                a.step = smp.index ? smp.index[e] : 0;
+                a.token_out = m.picks.p + e; a.logprob_out = m.logprobs.p + e;
+                a.staged = row_smem ? 1 : 0;
+                if (sample_keys_in_registers(V)) sample_kernel<32><<<1, kSampleThreads, row_smem, g_stream>>>(a);
+                else sample_kernel<0><<<1, kSampleThreads, row_smem, g_stream>>>(a);
+                LAUNCHED();
+            }
+        }
+    }
+    CK(cudaEventRecord(m.ev1, g_stream));
+    if (smp.on) {
+        CK(cudaMemcpyAsync(smp.out_tokens, m.picks.p, (size_t)E * sizeof(int), cudaMemcpyDeviceToHost, g_stream));
+        if (smp.out_logprobs) CK(cudaMemcpyAsync(smp.out_logprobs, m.logprobs.p, (size_t)E * sizeof(float), cudaMemcpyDeviceToHost, g_stream));
+    } else if (n_want > 0 && logits_host) {
+        CK(cudaMemcpyAsync(logits_host, m.logits.p, (size_t)n_want * V * sizeof(float), cudaMemcpyDeviceToHost, g_stream));
+    }
+    CK(cudaStreamSynchronize(g_stream));
+    CK(cudaEventElapsedTime(&m.last_ms, m.ev0, m.ev1));
+    for (int e = 0; e < E; ++e) m.seqs[seqs[e]].len += counts[e];
+    return 0;
+}
+
+int open_seq(Model& m, int32_t* seq) {
+    for (size_t s = 0; s < m.seqs.size(); ++s)
+        if (!m.seqs[s].live) {
+            m.seqs[s].live = true;
+            m.seqs[s].len = 0;
+            m.seqs[s].pages.clear();
+            *seq = (int32_t)s;
+            return 0;
+        }
+    return fail("no free state slot (%zu sequences live)", m.seqs.size());
+}
+int close_seq(Model& m, int32_t seq) {
+    if (seq < 0 || seq >= (int)m.seqs.size() || !m.seqs[seq].live) return fail("close: sequence %d is not open", seq);
+    SeqState& s = m.seqs[seq];
+    for (int p : s.pages) m.free_pages.push_back(p);
+    s.pages.clear();
+    s.len = 0;
+    s.live = false;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ti_seq_last_error(void) { return g_err.c_str(); }
+uint64_t ti_seq_launch_count(void) { return g_launches; }
+
+int ti_seq_init(int device) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) return fail("ti_seq_init: no CUDA device (this engine has no CPU fallback)");
+    if (device < 0 || device >= n) return fail("ti_seq_init: device %d of %d", device, n);
+    CK(cudaSetDevice(device));
+    cudaDeviceProp p{};
+    CK(cudaGetDeviceProperties(&p, device));
+    if (p.major < 10) return fail("ti_seq_init: device %d is sm_%d%d; this library is built for sm_100a only", device, p.major, p.minor);
+    g_num_sms = p.multiProcessorCount;
+    g_smem_optin = std::min<size_t>(p.sharedMemPerBlockOptin, 200 * 1024);
+    if (!g_stream) CK(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
+    CK(cudaFuncSetAttribute(gemv_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(gemv_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(wkv_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
+    CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
+    g_device = device;
+    return 0;
+}
+
+int ti_seq_model_new(const ti_seq_model_desc* desc, const ti_seq_layer_desc* layers, ti_seq_model_t* out) {
+    if (g_device < 0) return fail("ti_seq: not initialised -- call ti_seq_init(device) first (no CPU fallback exists)");
+    if (!desc || !layers || !out) return fail("model_new: null argument");
+    if (desc->vocab <= 0 || desc->width <= 0 || desc->n_layers <= 0) return fail("model_new: vocab %d width %d layers %d", desc->vocab, desc->width, desc->n_layers);
+    if (desc->mode != TI_SEQ_BF16 && desc->mode != TI_SEQ_F32) return fail("model_new: mode %d", desc->mode);
+    if (desc->max_tokens <= 0 || desc->max_seqs <= 0) return fail("model_new: max_tokens %d max_seqs %d", desc->max_tokens, desc->max_seqs);
+    if (desc->loop_times > 0 && (desc->loop_start < 0 || desc->loop_stop > desc->n_layers || desc->loop_start >= desc->loop_stop))
+        return fail("model_new: looped block [%d, %d) of %d layers", desc->loop_start, desc->loop_stop, desc->n_layers);
+    auto m = std::make_unique<Model>();
+    m->d = *desc;
+    m->wsize = desc->mode == TI_SEQ_BF16 ? 2 : 4;
+    m->layers.resize(desc->n_layers);
+    for (int i = 0; i < desc->n_layers; ++i) m->layers[i].d = layers[i];
+    TRY(describe_tensors(*m));
+    // the order of layer runs
+    auto add_run = [&](int layer, bool enters) {
+        m->runs.emplace_back();
+        m->runs.back().layer = layer;
+        m->runs.back().enters_pass = enters;
+    };
+    if (desc->loop_times > 0) {
+        for (int i = 0; i < desc->loop_start; ++i) add_run(i, false);
+        for (int t = 0; t < desc->loop_times; ++t)
+            for (int i = desc->loop_start; i < desc->loop_stop; ++i) add_run(i, i == desc->loop_start);
+        for (int i = desc->loop_stop; i < desc->n_layers; ++i) add_run(i, false);
+    } else {
+        for (int i = 0; i < desc->n_layers; ++i) add_run(i, false);
+    }
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_models.push_back(std::move(m));
+    *out = g_models.size();
+    return 0;
+}
+
+int ti_seq_model_tensor_count(ti_seq_model_t h, int32_t* n) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    *n = (int32_t)m->order.size();
+    return 0;
+}
+int ti_seq_model_tensor_info(ti_seq_model_t h, int32_t i, char* name, size_t cap, int64_t* shape, int32_t* ndim) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    if (i < 0 || i >= (int)m->order.size()) return fail("tensor index %d", i);
+    const std::string& nm = m->order[i];
+    snprintf(name, cap, "%s", nm.c_str());
+    const Tensor& t = m->tensors[nm];
+    *ndim = (int32_t)t.shape.size();
+    for (size_t k = 0; k < t.shape.size(); ++k) shape[k] = t.shape[k];
+    return 0;
+}
+
+static int check_shape(const Tensor& t, const char* name, const int64_t* shape, int32_t ndim) {
+    bool ok = (size_t)ndim == t.shape.size();
+    for (int k = 0; ok && k < ndim; ++k) ok = shape[k] == t.shape[k];
+    if (!ok) {
+        std::string want, got;
+        for (auto s : t.shape) want += std::to_string(s) + " ";
+        for (int k = 0; k < ndim; ++k) got += std::to_string(shape[k]) + " ";
+        return fail("tensor %s: shape [ %s] given, [ %s] expected", name, got.c_str(), want.c_str());
+    }
+    return 0;
+}
+
+int ti_seq_model_set_tensor(ti_seq_model_t h, const char* name, int32_t dtype, const void* data, const int64_t* shape, int32_t ndim) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    if (m->finalized) return fail("set_tensor after finalize");
+    auto it = m->tensors.find(name);
+    if (it == m->tensors.end()) return fail("tensor %s is not part of this model", name);
+    Tensor& t = it->second;
+    TRY(check_shape(t, name, shape, ndim));
+    const size_t n = t.count();
+    if (dtype == TI_SEQ_BF16 && t.matrix && m->d.mode == TI_SEQ_BF16) {   // stays as it is
+        TRY(t.data.alloc(n * 2));
+        CK(cudaMemcpyAsync(t.data.p, data, n * 2, cudaMemcpyHostToDevice, g_stream));
+        CK(cudaStreamSynchronize(g_stream));
+        t.set = true;
+        return 0;
+    }
+    DevBuf<float> f;
+    TRY(f.alloc(n));
+    if (dtype == TI_SEQ_BF16) {
+        DevBuf<__nv_bfloat16> b;
+        TRY(b.alloc(n));
+        CK(cudaMemcpyAsync(b.p, data, n * 2, cudaMemcpyHostToDevice, g_stream));
+        bf16_to_f32_kernel<<<grid_for(n), 256, 0, g_stream>>>(b.p, f.p, n);
+        LAUNCHED();
+        CK(cudaStreamSynchronize(g_stream));
+    } else if (dtype == TI_SEQ_F32) {
+        CK(cudaMemcpyAsync(f.p, data, n * 4, cudaMemcpyHostToDevice, g_stream));
+    } else {
+        return fail("tensor %s: element type %d", name, dtype);
+    }
+    return store_from_f32(*m, t, f.p, n);
+}
+
+int ti_seq_model_set_tensor_synthetic(ti_seq_model_t h, const char* name, const int64_t* shape, int32_t ndim, uint64_t seed, float amp, float offset) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    if (m->finalized) return fail("set_tensor after finalize");
+    auto it = m->tensors.find(name);
+    if (it == m->tensors.end()) return fail("tensor %s is not part of this model", name);
+    Tensor& t = it->second;
+    TRY(check_shape(t, name, shape, ndim));
+    const size_t n = t.count();
+    DevBuf<float> f;
+    TRY(f.alloc(n));
+    synth_fill_f32_kernel<<<grid_for(n), 256, 0, g_stream>>>(f.p, n, seed, amp, offset);
+    LAUNCHED();
+    return store_from_f32(*m, t, f.p, n);
+}
+
+int ti_seq_model_finalize(ti_seq_model_t h) {
+    Model* mp = get_model(h);
+    if (!mp) return fail("bad model handle");
+    Model& m = *mp;
+    if (m.finalized) return 0;
+    for (const auto& nm : m.order)
+        if (!m.tensors[nm].set) return fail("finalize: tensor %s was not given", nm.c_str());
+    auto T = [&](const std::string& nm) -> Tensor* {
+        auto it = m.tensors.find(nm);
+        return it == m.tensors.end() ? nullptr : &it->second;
+    };
+    auto F = [&](const std::string& nm) -> const float* { return reinterpret_cast<const float*>(T(nm)->data.p); };
+    auto P = [&](const std::string& nm) -> const void* { return T(nm)->data.p; };
+    const int D = m.d.width;
+    m.embed = P("embed");
+    m.head = P("head");
+    m.final_norm = F("final.norm");
+    if (m.d.loop_times > 0) m.loop_in = P("loop.in");
+    for (int i = 0; i < m.d.n_layers; ++i) {
+        LayerW& L = m.layers[i];
+        const std::string p = "l" + std::to_string(i) + ".";
+        L.norm1 = F(p + "norm1");
+        L.norm1b = F(p + "norm1b");
+        if (L.d.mixer == TI_SEQ_MIXER_ATTENTION) {
+            TRY(concat_rows(m, {T(p + "mix.q"), T(p + "mix.k"), T(p + "mix.v"), L.d.out_gate ? T(p + "mix.g") : nullptr}, L.qkvg_buf, &L.n_qkvg));
+            L.qkvg = L.qkvg_buf.p;
+            for (const char* s : {"mix.q", "mix.k", "mix.v", "mix.g"})
+                if (T(p + s)) T(p + s)->data.release();
+            L.o = P(p + "mix.o");
+            const std::vector<float> f = rotary_frequencies(L.d);
+            TRY(L.inv_freq.alloc(std::max<size_t>(1, f.size())));
+            if (!f.empty()) CK(cudaMemcpy(L.inv_freq.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
+            m.max_proj = std::max(m.max_proj, L.n_qkvg);
+            m.max_att = std::max(m.max_att, L.d.heads * L.d.vdim);
+        } else {
+            const int C = L.d.heads * L.d.dim;
+            L.r = P(p + "mix.r"); L.k = P(p + "mix.k"); L.v = P(p + "mix.v"); L.g = P(p + "mix.g");
+            L.w1 = P(p + "mix.w1"); L.w2 = P(p + "mix.w2"); L.o = P(p + "mix.o");
+            L.w0 = F(p + "mix.w0"); L.u = F(p + "mix.u"); L.normw = F(p + "mix.norm");
+            TRY(L.mu.alloc(5 * (size_t)D));
+            int k = 0;
+            for (const char* s : {"r", "k", "v", "g", "w"})
+                CK(cudaMemcpy(L.mu.p + (size_t)(k++) * D, F(p + "mix.mu." + s), (size_t)D * sizeof(float), cudaMemcpyDeviceToDevice));
+            m.max_proj = std::max(m.max_proj, 5 * C);
+            m.max_att = std::max(m.max_att, C);
+            m.max_rank = std::max(m.max_rank, L.d.decay_rank);
+            m.any_wkv = true;
+        }
+        if (L.d.ff > 0) {
+            int rows = 0;
+            TRY(concat_rows(m, {T(p + "mlp.gate"), T(p + "mlp.up")}, L.gateup_buf, &rows));
+            L.gateup = L.gateup_buf.p;
+            T(p + "mlp.gate")->data.release();
+            T(p + "mlp.up")->data.release();
+            L.down = P(p + "mlp.down");
+            L.norm2 = F(p + "norm2");
+            L.norm2b = F(p + "norm2b");
+            m.max_proj = std::max(m.max_proj, 2 * L.d.ff);
+            m.max_ff = std::max(m.max_ff, L.d.ff);
+        }
+    }
+    // cache pools and state slots: one of each per layer RUN
+    m.num_pages = (m.d.max_tokens + kPageTokens - 1) / kPageTokens;
+    for (int p = m.num_pages - 1; p >= 0; --p) m.free_pages.push_back(p);
+    m.seqs.resize(m.d.max_seqs);
+    for (Run& R : m.runs) {
+        const ti_seq_layer_desc& L = m.layers[R.layer].d;
+        if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
+            TRY(R.k_pool.alloc((size_t)m.num_pages * kPageTokens * L.kv_heads * L.dim));
+            TRY(R.v_pool.alloc((size_t)m.num_pages * kPageTokens * L.kv_heads * L.vdim));
+        } else {
+            TRY(R.state.alloc((size_t)m.d.max_seqs * L.heads * L.dim * L.dim));
+            TRY(R.prev.alloc((size_t)m.d.max_seqs * D));
+            CK(cudaMemset(R.state.p, 0, R.state.n * sizeof(float)));
+            CK(cudaMemset(R.prev.p, 0, R.prev.n * sizeof(float)));
+        }
+    }
+    CK(cudaEventCreate(&m.ev0));
+    CK(cudaEventCreate(&m.ev1));
+    m.finalized = true;
+    return 0;
+}
+
+int ti_seq_model_free(ti_seq_model_t h) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (h == 0 || h > g_models.size() || !g_models[h - 1]) return fail("bad model handle");
+    cudaStreamSynchronize(g_stream);
+    g_models[h - 1].reset();
+    return 0;
+}
+
+int ti_seq_open(ti_seq_model_t h, int32_t* seq) {
+    Model* m = get_model(h);
+    if (!m || !m->finalized) return fail("bad model handle");
+    return open_seq(*m, seq);
+}
+int ti_seq_close(ti_seq_model_t h, int32_t seq) {
+    Model* m = get_model(h);
+    if (!m || !m->finalized) return fail("bad model handle");
+    return close_seq(*m, seq);
+}
+int ti_seq_length(ti_seq_model_t h, int32_t seq, int32_t* tokens) {
+    Model* m = get_model(h);
+    if (!m || !m->finalized) return fail("bad model handle");
+    if (seq < 0 || seq >= (int)m->seqs.size() || !m->seqs[seq].live) return fail("sequence %d is not open", seq);
+    *tokens = m->seqs[seq].len;
+    return 0;
+}
+int ti_seq_pool_info(ti_seq_model_t h, int32_t* free_pages, int32_t* total_pages, int32_t* free_slots, int32_t* page_tokens) {
+    Model* m = get_model(h);
+    if (!m || !m->finalized) return fail("bad model handle");
+    int fs = 0;
+    for (const auto& s : m->seqs) fs += !s.live;
+    if (free_pages) *free_pages = (int32_t)m->free_pages.size();
+    if (total_pages) *total_pages = m->num_pages;
+    if (free_slots) *free_slots = fs;
+    if (page_tokens) *page_tokens = kPageTokens;
+    return 0;
+}
+int ti_seq_pages(ti_seq_model_t h, int32_t seq, int32_t* pages, int32_t cap, int32_t* n) {
+    Model* m = get_model(h);
+    if (!m || !m->finalized) return fail("bad model handle");
+    if (seq < 0 || seq >= (int)m->seqs.size() || !m->seqs[seq].live) return fail("sequence %d is not open", seq);
+    const auto& pg = m->seqs[seq].pages;
+    *n = (int32_t)pg.size();
+    for (int i = 0; i < (int)pg.size() && i < cap; ++i) pages[i] = pg[i];
+    return 0;
+}
+
+int ti_seq_step(ti_seq_model_t h, int32_t n_entries, const int32_t* seqs, const int32_t* counts, const int32_t* tokens, int32_t n_want,
+                const int32_t* want_rows, float* logits_host) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    return run_step(*m, n_entries, seqs, counts, tokens, n_want, want_rows, logits_host, SampleSpec{});
+}
+
+int ti_seq_step_sample(ti_seq_model_t h, int32_t n_entries, const int32_t* seqs, const int32_t* counts, const int32_t* tokens, float temperature,
+                       int32_t top_k, float top_p, uint64_t seed, const int32_t* sample_index, int32_t* out_tokens, float* out_logprobs) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    if (!out_tokens) return fail("step_sample: out_tokens is null");
+    SampleSpec s;
+    s.on = true; s.temperature = temperature; s.top_k = top_k; s.top_p = top_p; s.seed = seed; s.index = sample_index;
+    s.out_tokens = out_tokens; s.out_logprobs = out_logprobs;
+    return run_step(*m, n_entries, seqs, counts, tokens, 0, nullptr, nullptr, s);
+}
+
+// The generation loop: continuous batching over the step above.  Waiting requests are admitted in order while a state slot is
+// free and the pool has pages for the whole request (prompt + max_new, so that a running request never stalls); a step takes
+// one decode token from every running request whose prompt is done, then prompt portions (oldest first) until `step_tokens`
+// rows are filled.
+int ti_seq_generate(ti_seq_model_t h, int32_t n_req, const int32_t* prompts, const int32_t* lens, int32_t max_new, int32_t step_tokens,
+                    float temperature, int32_t top_k, float top_p, uint64_t seed, int32_t eos, int32_t* out_tokens, int32_t* out_lens) {
+    Model* mp = get_model(h);
+    if (!mp || !mp->finalized) return fail("bad model handle");
+    Model& m = *mp;
+    if (n_req <= 0 || max_new <= 0) return fail("generate: n_req %d max_new %d", n_req, max_new);
+    if (step_tokens <= 0) step_tokens = 512;
+    struct Req { int id, seq, fed, n_out, last, reserved; const int32_t* prompt; int len; };
+    std::vector<size_t> start(n_req + 1, 0);
+    for (int i = 0; i < n_req; ++i) {
+        if (lens[i] <= 0) return fail("generate: request %d has an empty prompt", i);
+        start[i + 1] = start[i] + lens[i];
+    }
+    const auto pages_for = [](int tokens) { return (tokens + kPageTokens - 1) / kPageTokens; };
+    for (int i = 0; i < n_req; ++i)
+        if (pages_for(lens[i] + max_new) > m.num_pages) return fail("generate: request %d (%d + %d tokens) exceeds the page pool", i, lens[i], max_new);
+    std::vector<Req> running;
+    int next = 0, done = 0, reserved_pages = 0;
+    for (int i = 0; i < n_req; ++i) out_lens[i] = 0;
+    std::vector<int32_t> seqs, counts, toks, sidx, picks;
+    while (done < n_req) {
+        // admission
+        while (next < n_req) {
+            const int need = pages_for(lens[next] + max_new);
+            int live_pages = 0;
+            for (const auto& s : m.seqs) live_pages += s.live ? (int)s.pages.size() : 0;
+            (void)live_pages;
+            if (reserved_pages + need > m.num_pages) break;
+            int32_t s = -1;
+            if (open_seq(m, &s) != 0) break;
+            running.push_back(Req{next, s, 0, 0, 0, need, prompts + start[next], lens[next]});
+            reserved_pages += need;
+            ++next;
+        }
+        if (running.empty()) return fail("generate: nothing can be admitted");
+        seqs.clear(); counts.clear(); toks.clear(); sidx.clear();
+        int budget = step_tokens;
+        std::vector<int> in_step;
+        for (size_t i = 0; i < running.size(); ++i)   // decode tokens first
+            if (running[i].fed == running[i].len && budget > 0) {
+                seqs.push_back(running[i].seq); counts.push_back(1); toks.push_back(running[i].last); sidx.push_back(running[i].n_out);
+                in_step.push_back((int)i);
+                --budget;
+            }
+        for (size_t i = 0; i < running.size() && budget > 0; ++i)
+            if (running[i].fed < running[i].len) {
+                const int c = std::min(budget, running[i].len - running[i].fed);
+                seqs.push_back(running[i].seq); counts.push_back(c); sidx.push_back(0);
+                toks.insert(toks.end(), running[i].prompt + running[i].fed, running[i].prompt + running[i].fed + c);
+                in_step.push_back((int)i);
+                budget -= c;
+            }
+        picks.resize(seqs.size());
+        SampleSpec s;
+        s.on = true; s.temperature = temperature; s.top_k = top_k; s.top_p = top_p; s.seed = seed; s.index = sidx.data(); s.out_tokens = picks.data();
+        TRY(run_step(m, (int)seqs.size(), seqs.data(), counts.data(), toks.data(), 0, nullptr, nullptr, s));
+        std::vector<size_t> finished;
+        for (size_t k = 0; k < in_step.size(); ++k) {
+            Req& r = running[in_step[k]];
+            const bool was_decode = r.fed == r.len;
+            if (!was_decode) r.fed += counts[k];
+            if (r.fed < r.len) continue;   // the pick behind an unfinished prompt portion is not used
+            r.last = picks[k];
+            out_tokens[(size_t)r.id * max_new + r.n_out] = picks[k];
+            ++r.n_out;
+            out_lens[r.id] = r.n_out;
+            if (r.n_out >= max_new || (eos >= 0 && picks[k] == eos)) finished.push_back(in_step[k]);
+        }
+        std::sort(finished.rbegin(), finished.rend());
+        for (size_t i : finished) {
+            TRY(close_seq(m, running[i].seq));
+            reserved_pages -= running[i].reserved;
+            running.erase(running.begin() + i);
+            ++done;
+        }
+    }
+    return 0;
+}
+
+int ti_seq_debug_layers(ti_seq_model_t h, int32_t enable) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    m->dbg = enable != 0;
+    m->cap_rows = 0;   // scratch is laid out again on the next step
+    return 0;
+}
+int ti_seq_debug_layers_read(ti_seq_model_t h, float* out, size_t cap_floats, int32_t* runs, int32_t* rows) {
+    Model* m = get_model(h);
+    if (!m || !m->dbg || !m->dbg_buf.p) return fail("debug layers are not enabled");
+    const size_t n = m->runs.size() * (size_t)m->dbg_rows * m->d.width;
+    if (n > cap_floats) return fail("debug buffer too small: %zu floats needed", n);
+    CK(cudaMemcpy(out, m->dbg_buf.p, n * sizeof(float), cudaMemcpyDeviceToHost));
+    *runs = (int32_t)m->runs.size();
+    *rows = m->dbg_rows;
+    return 0;
+}
+int ti_seq_last_step_ms(ti_seq_model_t h, float* ms) {
+    Model* m = get_model(h);
+    if (!m) return fail("bad model handle");
+    *ms = m->last_ms;
+    return 0;
+}
+int ti_seq_model_bytes(ti_seq_model_t h, double* weight_bytes, double* kv_bytes_per_token, double* state_bytes_per_seq) {
+    Model* m = get_model(h);
+    if (!m || !m->finalized) return fail("bad model handle");
+    double w = 0, kv = 0, st = 0;
+    const double D = m->d.width, ws = (double)m->wsize;
+    if (m->d.loop_times > 0) w += 2 * D * D * ws * m->d.loop_times;
+    for (const Run& R : m->runs) {
+        const ti_seq_layer_desc& L = m->layers[R.layer].d;
+        if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
+            w += ((double)L.heads * L.dim + (double)L.kv_heads * (L.dim + L.vdim) + (L.out_gate ? L.heads : 0) + (double)L.heads * L.vdim) * D * ws;
+            kv += (double)L.kv_heads * (L.dim + L.vdim) * 4;
+        } else {
+            const double C = (double)L.heads * L.dim;
+            w += (5 * C * D + (double)L.decay_rank * (D + C)) * ws;
+            st += ((double)L.heads * L.dim * L.dim + D) * 4;
+        }
+        if (L.ff > 0) w += 3.0 * L.ff * D * ws;
+    }
+    w += (double)m->d.vocab * D * ws;
+    if (weight_bytes) *weight_bytes = w;
+    if (kv_bytes_per_token) *kv_bytes_per_token = kv;
+    if (state_bytes_per_seq) *state_bytes_per_seq = st;
+    return 0;
+}
+
+}  // extern "C"

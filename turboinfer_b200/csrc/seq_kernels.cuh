@@ -1,0 +1,509 @@
+// seq_kernels.cuh -- kernels of the layered sequence engine (seq_engine.cu): a decoder described layer by layer (windowed
+// rotary attention with unit-RMS queries / keys and a per-head output gate, token-shifted linear recurrence with a
+// data-dependent decay, gated feed-forward, scalar-gain RMS norms before and after every sublayer, a looped block of
+// layers) stepping a RAGGED batch: the rows of a step are the new tokens of several sequences, portions of prompts next
+// to single decoded tokens.  Every row carries (sequence entry, position); attention reads a paged key/value cache through
+// the sequence's page table, the recurrence reads and writes the sequence's state slot.
+//
+// Number formats.  The residual stream, norms, rotary angles, attention scores and weights, the recurrent state, decays,
+// gates of the recurrence and unit norms are fp32 in both modes.  WT = __nv_bfloat16: matrix products take bf16 weights and
+// bf16-rounded activations with fp32 accumulation (tensor cores); WT = float: true fp32 FMA products (no TF32).
+#pragma once
+#include <cuda_bf16.h>
+#include <cstdint>
+#include "kernels.cuh"
+
+namespace tib {
+namespace seq {
+
+constexpr int kPageTokens = 64;
+
+// what a step's kernels need to find a row's sequence: all arrays live in one device buffer uploaded once per step
+struct StepMeta {
+    const int* tok;        // [T] token id of every row
+    const int* row_ent;    // [T] entry (sequence of this step) of every row
+    const int* row_pos;    // [T] position of the row's token in its sequence
+    const int* ent_row0;   // [E + 1] first row of every entry
+    const int* ent_slot;   // [E] state slot / page-table row of every entry
+    const int* ent_pos0;   // [E] position of the entry's first row (tokens already cached)
+    const int* page_table; // [slots][table_stride] physical page of every logical page
+    int table_stride;
+    int T, E;
+};
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+// activation as the matrix product sees it: rounded to the weight type
+template <typename WT> __device__ __forceinline__ float act_round(float v);
+template <> __device__ __forceinline__ float act_round<float>(float v) { return v; }
+template <> __device__ __forceinline__ float act_round<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// sum over the block (blockDim.x a multiple of 32, <= 1024); `red` holds 32 floats; every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float s = (l < nw) ? red[l] : 0.f;
+    s = warp_sum(s);
+    return s;
+}
+
+// ---- embedding -----------------------------------------------------------------------------------------------------
+// x[t] = embed[tok[t]]; x0 (optional) keeps the embedding output for the looped block's input projection
+template <typename WT>
+__global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, float* x0) {
+    const int t = blockIdx.x;
+    const WT* e = emb + (size_t)m.tok[t] * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = to_f32(e[d]);
+        x[(size_t)t * D + d] = v;
+        if (x0) x0[(size_t)t * D + d] = v;
+    }
+}
+// xc[t] = [x[t]; x0[t]]
+__global__ void concat_rows_kernel(const float* x, const float* x0, int D, float* xc) {
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        xc[(size_t)t * 2 * D + d] = x[(size_t)t * D + d];
+        xc[(size_t)t * 2 * D + D + d] = x0[(size_t)t * D + d];
+    }
+}
+
+// ---- RMS norm with one gain for all coordinates ----------------------------------------------------------------------
+// y[t] = x[row(t)] / sqrt(mean(x^2) + eps) * gain[0]; rows (optional) gathers (the rows whose logits are wanted)
+__global__ void scalar_rmsnorm_kernel(const float* x, const int* rows, int D, const float* gain, float eps, float* y) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[t] : t) * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) ss += xr[d] * xr[d];
+    ss = block_sum(ss, red);
+    const float sc = gain[0] / sqrtf(ss / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = xr[d] * sc;
+}
+// x[t] += m[t] / sqrt(mean(m^2) + eps) * gain[0]   (the norm behind a sublayer, then the residual sum);
+// with gain2 != null it also writes the next sublayer's input y[t] = x[t] / rms(x[t]) * gain2[0]
+__global__ void postnorm_residual_kernel(float* x, const float* mo, int D, const float* gain, float eps, const float* gain2, float* y) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const float* mr = mo + (size_t)t * D;
+    float* xr = x + (size_t)t * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) ss += mr[d] * mr[d];
+    ss = block_sum(ss, red);
+    const float sc = gain[0] / sqrtf(ss / (float)D + eps);
+    float s2 = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = xr[d] + mr[d] * sc;
+        xr[d] = v;
+        s2 += v * v;
+    }
+    if (gain2) {
+        s2 = block_sum(s2, red);
+        const float sc2 = gain2[0] / sqrtf(s2 / (float)D + eps);
+        for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = xr[d] * sc2;
+    }
+}
+
+// ---- matrix products: C[M, N] = epi(A[M, K] . W[N, K]^T) ----------------------------------------------------------------
+enum { EPI_NONE = 0, EPI_TANH = 1, EPI_SCALE = 2, EPI_SILU = 3 };
+__device__ __forceinline__ float epi_apply(float v, int epi, float alpha) {
+    if (epi == EPI_TANH) return tanhf(v);
+    if (epi == EPI_SCALE) return v * alpha;
+    if (epi == EPI_SILU) return v / (1.f + expf(-v));
+    return v;
+}
+
+// true fp32: 64 x 64 tile, 16-deep k-steps, 256 threads with 4 x 4 outputs each
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const float* A, int lda, const float* W, float* C, int ldc, int M, int N, int K,
+                                                        int epi, float alpha) {
+    __shared__ float As[16][64 + 4], Ws[16][64 + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int r = i >> 4, c = i & 15;
+            const int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+            As[c][r] = (gm < M && gk < K) ? A[(size_t)gm * lda + gk] : 0.f;
+            Ws[c][r] = (gn < N && gk < K) ? W[(size_t)gn * K + gk] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+            if (gm < M && gn < N) C[(size_t)gm * ldc + gn] = epi_apply(acc[i][j], epi, alpha);
+        }
+}
+
+// bf16 x bf16 -> fp32 on the warp-level tensor path (mma.sync m16n8k16): 64 x 64 tile, 32-deep k-steps, 4 warps of 32 x 32.
+// A is fp32 in memory and rounded to bf16 while it is staged; any M, N, K (edges are zero-filled).
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__global__ void __launch_bounds__(128) gemm_bf16_kernel(const float* A, int lda, const __nv_bfloat16* W, float* C, int ldc, int M, int N,
+                                                         int K, int epi, float alpha) {
+    constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;
+    __shared__ __align__(16) __nv_bfloat16 As[BM * LD], Ws[BN * LD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const bool vecA = (lda % 4 == 0) && (K % BK == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    const bool vecW = (K % BK == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
+    float acc[2][4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        if (vecA) {
+            for (int i = threadIdx.x; i < BM * (BK / 4); i += 128) {
+                const int r = i / (BK / 4), c = (i % (BK / 4)) * 4;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (m0 + r < M) v = *reinterpret_cast<const float4*>(A + (size_t)(m0 + r) * lda + k0 + c);
+                __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(&As[r * LD + c]);
+                d[0] = __floats2bfloat162_rn(v.x, v.y);
+                d[1] = __floats2bfloat162_rn(v.z, v.w);
+            }
+        } else {
+            for (int i = threadIdx.x; i < BM * BK; i += 128) {
+                const int r = i / BK, c = i % BK;
+                As[r * LD + c] = __float2bfloat16_rn((m0 + r < M && k0 + c < K) ? A[(size_t)(m0 + r) * lda + k0 + c] : 0.f);
+            }
+        }
+        if (vecW) {
+            for (int i = threadIdx.x; i < BN * (BK / 8); i += 128) {
+                const int r = i / (BK / 8), c = (i % (BK / 8)) * 8;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (n0 + r < N) v = *reinterpret_cast<const uint4*>(W + (size_t)(n0 + r) * K + k0 + c);
+                *reinterpret_cast<uint4*>(&Ws[r * LD + c]) = v;
+            }
+        } else {
+            for (int i = threadIdx.x; i < BN * BK; i += 128) {
+                const int r = i / BK, c = i % BK;
+                Ws[r * LD + c] = (n0 + r < N && k0 + c < K) ? W[(size_t)(n0 + r) * K + k0 + c] : __float2bfloat16_rn(0.f);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk += 16) {
+            uint32_t a[2][4], b[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat16* p = &As[(wm + i * 16 + g) * LD + kk + 2 * t4];
+                a[i][0] = *reinterpret_cast<const uint32_t*>(p);
+                a[i][1] = *reinterpret_cast<const uint32_t*>(p + 8 * LD);
+                a[i][2] = *reinterpret_cast<const uint32_t*>(p + 8);
+                a[i][3] = *reinterpret_cast<const uint32_t*>(p + 8 * LD + 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat16* p = &Ws[(wn + j * 8 + g) * LD + kk + 2 * t4];
+                b[j][0] = *reinterpret_cast<const uint32_t*>(p);
+                b[j][1] = *reinterpret_cast<const uint32_t*>(p + 8);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], a[i], b[j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int gm = m0 + wm + i * 16 + g + (e >> 1) * 8, gn = n0 + wn + j * 8 + 2 * t4 + (e & 1);
+                if (gm < M && gn < N) C[(size_t)gm * ldc + gn] = epi_apply(acc[i][j][e], epi, alpha);
+            }
+}
+
+// few rows (M <= 8, the decode step): the weights are streamed once, one warp per output column; the rows sit in shared
+// memory (rounded to the weight type).  Bound by the weight bytes.
+constexpr int kGemvMaxRows = 8;
+template <typename WT>
+__global__ void __launch_bounds__(256) gemv_rows_kernel(const float* A, int lda, const WT* W, float* C, int ldc, int M, int N, int K, int epi,
+                                                         float alpha) {
+    extern __shared__ float xs[];   // [M][K]
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = act_round<WT>(A[(size_t)(i / K) * lda + (i % K)]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
+        const WT* w = W + (size_t)n * K;
+        float acc[kGemvMaxRows];
+#pragma unroll
+        for (int r = 0; r < kGemvMaxRows; ++r) acc[r] = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_f32(w[k]);
+#pragma unroll
+            for (int r = 0; r < kGemvMaxRows; ++r)
+                if (r < M) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < kGemvMaxRows; ++r)
+            if (r < M) {
+                const float s = warp_sum(acc[r]);
+                if (lane == 0) C[(size_t)r * ldc + n] = epi_apply(s, epi, alpha);
+            }
+    }
+}
+
+// ---- attention -------------------------------------------------------------------------------------------------------
+struct AttnShape {
+    int heads, kv_heads, dim, vdim;   // H, G, d, dv
+    int window;                       // a row at position p sees positions p - window + 1 .. p (0: all of 0 .. p)
+    int rot_dims;                     // leading coordinates of a head that are rotated, in pairs (2i, 2i + 1)
+    int qk_norm, out_gate;
+    float scale, eps;
+    int ld;                           // row stride of the fused projection output [q | k | v | gate]
+};
+// Rotation of q and k, unit RMS per head, and the cache append: one block per row.  q is rewritten in place; k and v go
+// to the row's page.  inv_freq[rot_dims / 2] holds the (scaled) frequencies; the angle is position * frequency in fp32.
+__global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const float* inv_freq, float* k_pool, float* v_pool) {
+    const int t = blockIdx.x;
+    const int pos = m.row_pos[t];
+    const int slot = m.ent_slot[m.row_ent[t]];
+    const int page = m.page_table[(size_t)slot * m.table_stride + pos / kPageTokens];
+    const size_t tok_off = (size_t)page * kPageTokens + pos % kPageTokens;
+    float* row = qkvg + (size_t)t * s.ld;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int nqk = s.heads + s.kv_heads;
+    for (int h = warp; h < nqk; h += nw) {
+        float* v = row + (size_t)h * s.dim;   // q heads first, k heads right behind them
+        float ss = 0.f;
+        for (int i = lane; i < s.dim / 2 + (s.dim & 1); i += 32) {
+            float a = v[2 * i], b = (2 * i + 1 < s.dim) ? v[2 * i + 1] : 0.f;
+            if (2 * i + 1 < s.rot_dims) {
+                const float ang = (float)pos * inv_freq[i];
+                float sn, cs;
+                sincosf(ang, &sn, &cs);
+                const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+                a = ra;
+                b = rb;
+            }
+            v[2 * i] = a;
+            if (2 * i + 1 < s.dim) v[2 * i + 1] = b;
+            ss += a * a + b * b;
+        }
+        ss = warp_sum(ss);
+        const float sc = s.qk_norm ? 1.f / sqrtf(ss / (float)s.dim + s.eps) : 1.f;
+        __syncwarp();
+        if (h < s.heads) {
+            for (int i = lane; i < s.dim; i += 32) v[i] *= sc;
+        } else {
+            float* kd = k_pool + tok_off * (size_t)(s.kv_heads * s.dim) + (size_t)(h - s.heads) * s.dim;
+            for (int i = lane; i < s.dim; i += 32) kd[i] = v[i] * sc;
+        }
+    }
+    const float* vs = row + (size_t)nqk * s.dim;
+    float* vd = v_pool + tok_off * (size_t)(s.kv_heads * s.vdim);
+    for (int i = threadIdx.x; i < s.kv_heads * s.vdim; i += blockDim.x) vd[i] = vs[i];
+}
+
+// Softmax attention of one (row, query head) over the keys its window allows, read from the paged cache: 4 warps share the
+// keys, a lane owns coordinates lane, lane + 32, ...; online softmax per warp, merged through shared memory.  The output is
+// multiplied by sigmoid(gate) of its head.  out[t][h * dv ..].
+constexpr int kAttnWarps = 4;
+constexpr int kAttnMaxPerLane = 8;   // head sizes up to 256
+__global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const float* qkvg, StepMeta m, AttnShape s, const float* k_pool,
+                                                                            const float* v_pool, float* out) {
+    extern __shared__ float sm[];   // [kAttnWarps][dv] partial outputs, then [kAttnWarps] max, [kAttnWarps] sum
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = m.row_pos[t];
+    const int slot = m.ent_slot[m.row_ent[t]];
+    const int* table = m.page_table + (size_t)slot * m.table_stride;
+    const int g = h / (s.heads / s.kv_heads);
+    const float* q = qkvg + (size_t)t * s.ld + (size_t)h * s.dim;
+    float qr[kAttnMaxPerLane], o[kAttnMaxPerLane];
+#pragma unroll
+    for (int i = 0; i < kAttnMaxPerLane; ++i) {
+        const int d = lane + 32 * i;
+        qr[i] = d < s.dim ? q[d] : 0.f;
+        o[i] = 0.f;
+    }
+    const int lo = (s.window > 0 && pos - s.window + 1 > 0) ? pos - s.window + 1 : 0;
+    float mx = -INFINITY, l = 0.f;
+    const size_t kstride = (size_t)s.kv_heads * s.dim, vstride = (size_t)s.kv_heads * s.vdim;
+    for (int j = lo + warp; j <= pos; j += kAttnWarps) {
+        const size_t off = (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens;
+        const float* kr = k_pool + off * kstride + (size_t)g * s.dim;
+        float sc = 0.f;
+#pragma unroll
+        for (int i = 0; i < kAttnMaxPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < s.dim) sc = fmaf(qr[i], kr[d], sc);
+        }
+        sc = warp_sum(sc) * s.scale;
+        const float nm = fmaxf(mx, sc);
+        const float corr = expf(mx - nm), p = expf(sc - nm);
+        l = l * corr + p;
+        const float* vr = v_pool + off * vstride + (size_t)g * s.vdim;
+#pragma unroll
+        for (int i = 0; i < kAttnMaxPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < s.vdim) o[i] = fmaf(p, vr[d], o[i] * corr);
+        }
+        mx = nm;
+    }
+    float* po = sm;
+    float* pm = sm + kAttnWarps * s.vdim;
+    float* pl = pm + kAttnWarps;
+#pragma unroll
+    for (int i = 0; i < kAttnMaxPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < s.vdim) po[warp * s.vdim + d] = o[i];
+    }
+    if (lane == 0) {
+        pm[warp] = mx;
+        pl[warp] = l;
+    }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, pm[w]);
+    float L = 0.f, f[kAttnWarps];
+    for (int w = 0; w < kAttnWarps; ++w) {
+        f[w] = (pm[w] == -INFINITY) ? 0.f : expf(pm[w] - M);
+        L += pl[w] * f[w];
+    }
+    float gate = 1.f;
+    if (s.out_gate) {
+        const float z = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * s.dim + (size_t)s.kv_heads * s.vdim + h];
+        gate = 1.f / (1.f + expf(-z));
+    }
+    for (int d = threadIdx.x; d < s.vdim; d += blockDim.x) {
+        float acc = 0.f;
+        for (int w = 0; w < kAttnWarps; ++w) acc += po[w * s.vdim + d] * f[w];
+        out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc / L * gate;
+    }
+}
+
+// ---- gated feed-forward: act(gate) * up over the fused projection output [gate | up] ------------------------------------
+enum { ACT_RELU = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };
+__device__ __forceinline__ float ff_act(float z, int act) {
+    if (act == ACT_RELU) return fmaxf(z, 0.f);
+    if (act == ACT_SILU) return z / (1.f + expf(-z));
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__global__ void glu_kernel(const float* gu, int ff, int act, float* y, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / ff, c = i % ff;
+        y[i] = ff_act(gu[t * 2 * ff + c], act) * gu[t * 2 * ff + ff + c];
+    }
+}
+
+// ---- token-shifted linear recurrence (wkv) ----------------------------------------------------------------------------
+// mixes[s][t] = h[t] + (prev[t] - h[t]) * mu[s], s = r, k, v, g, w; prev is the row before within the entry, the slot's
+// saved row for an entry's first row, zeros at position 0.
+__global__ void wkv_mix_kernel(const float* h, StepMeta m, int D, const float* mu /*[5][D]*/, const float* prev_state /*[slots][D]*/,
+                               float* mixes /*[5][T][D]*/) {
+    const int t = blockIdx.x;
+    const int e = m.row_ent[t];
+    const bool first = (t == m.ent_row0[e]);
+    const float* pr = first ? (m.ent_pos0[e] > 0 ? prev_state + (size_t)m.ent_slot[e] * D : nullptr) : h + (size_t)(t - 1) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float hv = h[(size_t)t * D + d];
+        const float df = (pr ? pr[d] : 0.f) - hv;
+#pragma unroll
+        for (int s = 0; s < 5; ++s) mixes[((size_t)s * m.T + t) * D + d] = fmaf(df, mu[(size_t)s * D + d], hv);
+    }
+}
+// the slot keeps the mixer input of the entry's last row for the next step
+__global__ void wkv_save_prev_kernel(const float* h, StepMeta m, int D, float* prev_state) {
+    const int e = blockIdx.x;
+    const int t = m.ent_row0[e + 1] - 1;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) prev_state[(size_t)m.ent_slot[e] * D + d] = h[(size_t)t * D + d];
+}
+// The recurrence of one (entry, head), token by token: thread j owns column j of the state S [d][d] (key channel i, value
+// channel j).  o_j = sum_i r_i (S_ij + u_i k_i v_j); S_ij <- w_i S_ij + k_i v_j with w = exp(-exp(z + w0)).  The head's o is
+// divided by its RMS, multiplied by the channel weights and the gate.  S lives in shared memory while the entry's rows run
+// and goes back to the slot at the end (in global memory directly when it does not fit).
+struct WkvArgs {
+    const float *r, *k, *v, *gate, *z;   // [T][H * d] each (gate already through its activation)
+    const float *w0, *u, *normw;          // [H * d]
+    float* state;                         // [slots][H][d][d]
+    float* out;                           // [T][H * d]
+    int heads, dim;
+    float eps;
+    int s_in_smem;
+};
+__global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
+    extern __shared__ float sm[];
+    __shared__ float red[32];
+    const int e = blockIdx.x, hd = blockIdx.y, d = a.dim, j = threadIdx.x;
+    const int C = a.heads * d;
+    float* rs = sm;            // r_i
+    float* ks = rs + d;        // k_i
+    float* ws = ks + d;        // decay_i
+    float* us = ws + d;        // u_i * k_i
+    float* Sg = a.state + ((size_t)m.ent_slot[e] * a.heads + hd) * (size_t)d * d;
+    float* S = a.s_in_smem ? us + d : Sg;
+    const bool fresh = (m.ent_pos0[e] == 0);
+    if (j < d) {
+        if (a.s_in_smem)
+            for (int i = 0; i < d; ++i) S[i * d + j] = fresh ? 0.f : Sg[i * d + j];
+        else if (fresh)
+            for (int i = 0; i < d; ++i) S[i * d + j] = 0.f;
+    }
+    const int t0 = m.ent_row0[e], t1 = m.ent_row0[e + 1];
+    for (int t = t0; t < t1; ++t) {
+        const size_t base = (size_t)t * C + (size_t)hd * d;
+        __syncthreads();
+        if (j < d) {
+            const float kv = a.k[base + j];
+            rs[j] = a.r[base + j];
+            ks[j] = kv;
+            ws[j] = expf(-expf(a.z[base + j] + a.w0[hd * d + j]));
+            us[j] = a.u[hd * d + j] * kv;
+        }
+        __syncthreads();
+        float acc = 0.f;
+        if (j < d) {
+            const float vj = a.v[base + j];
+            for (int i = 0; i < d; ++i) {
+                const float s = S[i * d + j];
+                acc = fmaf(rs[i], fmaf(us[i], vj, s), acc);
+                S[i * d + j] = fmaf(ws[i], s, ks[i] * vj);
+            }
+        }
+        const float ss = block_sum(j < d ? acc * acc : 0.f, red);
+        if (j < d) a.out[base + j] = acc / sqrtf(ss / (float)d + a.eps) * a.normw[hd * d + j] * a.gate[base + j];
+    }
+    if (a.s_in_smem && j < d) {
+        __syncthreads();
+        for (int i = 0; i < d; ++i) Sg[i * d + j] = S[i * d + j];
+    }
+}
+
+// ---- helpers -----------------------------------------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float* x, const int* rows, int D, float* y) {
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = x[(size_t)rows[t] * D + d];
+}
+__global__ void f32_to_bf16_kernel(const float* x, __nv_bfloat16* y, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = __float2bfloat16_rn(x[i]);
+}
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16* x, float* y, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = __bfloat162float(x[i]);
+}
+
+}  // namespace seq
+}  // namespace tib

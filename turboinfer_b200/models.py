@@ -1,0 +1,114 @@
+"""Model registry: config.json's "architecture" picks the class that turns the configuration into an engine.
+
+    load_model(folder, dtype="bfloat16", max_tokens=..., max_seqs=...)
+
+reads folder/config.json and folder/model.safetensors.  Registered architectures:
+  * "Binusun"  -- layer list of windowed rotary attention / token-shifted linear recurrence (wkv) mixers with scalar-gain RMS
+                  norms around every sublayer, an optional looped block of layers; runs on the layered sequence engine
+                  (turboinfer_b200.seq, include/ti_b200_seq.h).
+  * "llama"    -- the quantized Llama-style decoder of the persistent decode kernel (turboinfer_b200.capi.Model); built from
+                  {"hidden", "layers", "heads", "inter", "vocab"} and fp32 tensors under the reference's names.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Callable, Dict, List, Tuple
+
+from . import seq as _seq
+
+REGISTRY: Dict[str, Callable] = {}
+
+
+def register(name: str):
+    def deco(fn):
+        REGISTRY[name] = fn
+        return fn
+    return deco
+
+
+def _req(d: dict, key: str, where: str):
+    if key not in d:
+        raise ValueError(f"config: {where} has no '{key}'")
+    return d[key]
+
+
+def binusun_descs(cfg: dict, mode: int, max_tokens: int, max_seqs: int, tensor_shapes: Dict[str, Tuple[int, ...]] = None):
+    """config.json of a Binusun model -> (ModelDesc, [LayerDesc]).  Sizes the configuration does not carry (the inner size of the
+    recurrence's decay projection) are taken from the checkpoint's tensor shapes."""
+    layers: List[_seq.LayerDesc] = []
+    for i, L in enumerate(_req(cfg, "layers", "the model")):
+        mx = _req(L, "mixer", f"layer {i}")
+        d = _seq.LayerDesc()
+        kind = _req(L, "type", f"layer {i}")
+        if kind == "attention":
+            d.mixer = _seq.MIXER_ATTENTION
+            d.heads, d.kv_heads = int(_req(mx, "heads", f"layer {i}")), int(_req(mx, "kv_heads", f"layer {i}"))
+            d.dim, d.vdim = int(_req(mx, "dim", f"layer {i}")), int(_req(mx, "vdim", f"layer {i}"))
+            d.window = int(_req(_req(mx, "mask", f"layer {i}"), "size", f"layer {i} mask"))
+            rot = _req(mx, "rot", f"layer {i}")
+            d.rot_dims, d.rot_base = int(_req(rot, "dims", f"layer {i} rot")), float(_req(rot, "base", f"layer {i} rot"))
+            sc = rot.get("scaling")
+            if sc:
+                d.rot_scaled = 1
+                d.rot_factor, d.rot_low = float(_req(sc, "factor", "rot.scaling")), float(_req(sc, "low", "rot.scaling"))
+                d.rot_high, d.rot_original = float(_req(sc, "high", "rot.scaling")), float(_req(sc, "original", "rot.scaling"))
+            d.qk_norm, d.out_gate = 1, 1
+            d.scale = float(_req(mx, "scale", f"layer {i}"))
+        elif kind == "wkv":
+            d.mixer = _seq.MIXER_WKV
+            d.heads, d.dim = int(_req(mx, "heads", f"layer {i}")), int(_req(mx, "dim", f"layer {i}"))
+            d.kv_heads, d.vdim = d.heads, d.dim
+            shape = (tensor_shapes or {}).get(f"l{i}.mix.w1")
+            if not shape:
+                raise ValueError(f"layer {i}: the decay projection l{i}.mix.w1 is missing from the checkpoint")
+            d.decay_rank = int(shape[0])
+        else:
+            raise ValueError(f"layer {i}: unknown mixer type '{kind}'")
+        mlp = L.get("mlp")
+        if mlp:
+            if mlp.get("kind", "dense") != "dense":
+                raise ValueError(f"layer {i}: unknown feed-forward kind '{mlp.get('kind')}'")
+            d.ff, d.ff_act = int(_req(mlp, "ff", f"layer {i} mlp")), _seq.ACT_RELU
+        layers.append(d)
+    m = _seq.ModelDesc()
+    m.vocab, m.width, m.n_layers = int(_req(cfg, "vocab", "the model")), int(_req(cfg, "width", "the model")), len(layers)
+    lp = cfg.get("loop")
+    if lp and int(lp.get("times", 0)) > 0 and int(lp["stop"]) > int(lp["start"]):
+        m.loop_start, m.loop_stop, m.loop_times = int(lp["start"]), int(lp["stop"]), int(lp["times"])
+    m.norm_eps = float(_req(_req(cfg, "norm", "the model"), "eps", "norm"))
+    m.logit_scale = float(cfg.get("logit_scale", 1.0))
+    m.mode, m.max_tokens, m.max_seqs = mode, int(max_tokens), int(max_seqs)
+    return m, layers
+
+
+@register("Binusun")
+def _load_binusun(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seqs: int):
+    mode = {"bfloat16": _seq.BF16, "float32": _seq.F32}[dtype]
+    shapes = {k: tuple(getattr(v, "shape", ())) for k, v in weights.items()}
+    desc, layers = binusun_descs(cfg, mode, max_tokens, max_seqs, shapes)
+    return _seq.SeqModel(desc, layers).load(weights)
+
+
+@register("llama")
+def _load_llama(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seqs: int):
+    import numpy as np
+
+    from . import capi
+    if dtype not in ("int4", "int8"):
+        raise ValueError("the llama decoder of this library runs INT4 / INT8 weights (dtype 'int4' or 'int8')")
+    capi.init(0)
+    meta = {k: int(cfg[k]) for k in ("vocab", "hidden", "layers", "heads", "inter")}
+    m = capi.Model(meta, capi.Q_INT4 if dtype == "int4" else capi.Q_INT8, attn_mode=1, rope_mode=1, max_seq=max_tokens)
+    return m.load({k: (v.to_f32() if isinstance(v, _seq.Bf16Array) else np.asarray(v, np.float32)) for k, v in weights.items()})
+
+
+def load_model(folder: str, dtype: str = "bfloat16", max_tokens: int = 4096, max_seqs: int = 4):
+    from .safetensors_io import read_safetensors
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    arch = cfg.get("architecture")
+    if arch not in REGISTRY:
+        raise ValueError(f"config.json: architecture '{arch}' is not registered (known: {sorted(REGISTRY)})")
+    weights = read_safetensors(os.path.join(folder, "model.safetensors"))
+    return REGISTRY[arch](cfg, weights, dtype, max_tokens, max_seqs)
