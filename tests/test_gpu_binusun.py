@@ -1,0 +1,295 @@
+"""The layered sequence engine on Binusun models against the plain implementation (tests/binusun_plain.py): every mechanism
+alone, prompts against token-by-token decoding, portions, ragged batches, reuse of pages and state slots, window / page
+edges, long decoding, odd sizes, and greedy generation through the engine's own generation loop."""
+import math
+
+import numpy as np
+import pytest
+
+import binusun_plain as plain
+from binusun_cases import attn_layer, build_engine, make_config, random_weights, rel_err, run_schedule, wkv_layer
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+LLAMA3 = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}
+
+
+def tokens(n, vocab, seed=1):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, n)]
+
+
+def whole(m, toks):
+    return run_schedule(m, {"a": toks}, [[("a", len(toks))]])["a"]
+
+
+# ---- each mechanism alone: residual stream after every layer run, and the logits -------------------------------------------
+MECHANISMS = {
+    "attention": make_config([attn_layer()]),
+    "attention_full_rot_scaled": make_config([attn_layer(rot_dims=32, scaling=LLAMA3, base=500.0)]),
+    "attention_mqa_vdim": make_config([attn_layer(heads=3, kv_heads=1, dim=24, vdim=40, rot_dims=8, window=5)]),
+    "attention_mha_window1": make_config([attn_layer(heads=2, kv_heads=2, window=1)]),
+    "wkv": make_config([wkv_layer()]),
+    "wkv_wide_heads": make_config([wkv_layer(heads=3, dim=40, rank=7)], width=56),
+    "feed_forward": make_config([attn_layer(ff=80), wkv_layer(ff=24)]),
+    "loop": make_config([wkv_layer(), attn_layer(ff=64), attn_layer(window=7), wkv_layer()], loop=(1, 3, 3)),
+    "loop_once_from_start": make_config([attn_layer(), wkv_layer(ff=32)], loop=(0, 1, 1)),
+    "no_loop_odd_sizes": make_config([wkv_layer(heads=1, dim=8, rank=1), attn_layer(heads=1, kv_heads=1, dim=10, vdim=6, rot_dims=4, ff=33)],
+                                     vocab=101, width=36, eps=1e-3, logit_scale=2.0),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(MECHANISMS))
+def test_mechanism_layers_and_logits(name, dtype):
+    cfg = MECHANISMS[name]
+    W = random_weights(cfg, seed=3)
+    toks = tokens(37, cfg["vocab"])
+    want, layers = plain.forward(cfg, W, toks, return_layers=True)
+    m = build_engine(cfg, W, dtype)
+    m.debug_layers(True)
+    got = whole(m, toks)
+    got_layers = m.read_layers(len(toks))
+    m.free()
+    assert got_layers.shape == layers.shape
+    for i in range(layers.shape[0]):
+        scale = np.sqrt((layers[i] ** 2).mean())
+        assert np.abs(got_layers[i] - layers[i]).max() / scale < TOL[dtype] * 5, f"layer run {i}"
+    assert rel_err(got, want) < TOL[dtype]
+
+
+def test_rotary_frequencies_bands():
+    # all three bands of the frequency scaling are present with these numbers: kept, blended, slowed down
+    f = plain.rotary_frequencies(32, 500.0, LLAMA3)
+    f0 = plain.rotary_frequencies(32, 500.0, None)
+    wl = 2 * math.pi / f0
+    assert (wl < 16).any() and (wl > 64).any() and ((wl >= 16) & (wl <= 64)).any()
+    assert np.allclose(f[wl < 16], f0[wl < 16]) and np.allclose(f[wl > 64], f0[wl > 64] / 8.0)
+
+
+# ---- prompts against decoding, portions, batches -----------------------------------------------------------------------------
+HYBRID = make_config([wkv_layer(ff=40), attn_layer(window=24, ff=64), attn_layer(window=70, rot_dims=32, scaling=LLAMA3), wkv_layer()], loop=(0, 3, 2))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefill_equals_token_by_token(dtype):
+    W = random_weights(HYBRID, seed=5)
+    toks = tokens(150, HYBRID["vocab"], 2)
+    want = plain.forward(HYBRID, W, toks)
+    m = build_engine(HYBRID, W, dtype)
+    a = whole(m, toks)
+    b = run_schedule(m, {"a": toks}, [[("a", 1)] for _ in toks])["a"]
+    m.free()
+    assert rel_err(a, want) < TOL[dtype] and rel_err(b, want) < TOL[dtype]
+    assert rel_err(b, a) < TOL[dtype]
+
+
+@pytest.mark.parametrize("sizes", [[2] * 40, [3, 61, 2, 64, 5, 65, 1, 63, 2], [64, 64, 64], [1, 127, 2, 2, 100], [129, 2, 33]])
+def test_portions(sizes):
+    W = random_weights(HYBRID, seed=6)
+    n = sum(sizes)
+    toks = tokens(n, HYBRID["vocab"], 3)
+    want = plain.forward(HYBRID, W, toks)
+    m = build_engine(HYBRID, W, "float32")
+    got = run_schedule(m, {"a": toks}, [[("a", c)] for c in sizes])["a"]
+    m.free()
+    assert rel_err(got, want) < TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_ragged_batch_equals_each_alone(dtype):
+    W = random_weights(HYBRID, seed=7)
+    reqs = {"a": tokens(131, 97, 4), "b": tokens(9, 97, 5), "c": tokens(70, 97, 6), "d": tokens(1, 97, 7)}
+    want = {k: plain.forward(HYBRID, W, v) for k, v in reqs.items()}
+    # portions of some next to single tokens of others; c joins late, d is a single token
+    sched = [[("a", 60), ("b", 2)], [("a", 1), ("b", 1), ("c", 33)], [("b", 1), ("a", 5), ("c", 2), ("d", 1)], [("a", 64), ("b", 5)],
+             [("c", 35), ("a", 1)]]
+    m = build_engine(HYBRID, W, dtype, max_tokens=512)
+    got = run_schedule(m, reqs, sched)
+    m.free()
+    for k in reqs:
+        assert rel_err(got[k], want[k]) < TOL[dtype], k
+
+
+def test_pages_and_slots_are_reused():
+    W = random_weights(HYBRID, seed=8)
+    m = build_engine(HYBRID, W, "float32", max_tokens=256, max_seqs=2)   # 4 pages, 2 slots
+    info = m.pool_info()
+    assert info["total_pages"] == 4 and info["free_slots"] == 2
+    seen_pages, seen_slots = [], []
+    for r in range(5):   # every round fills the pool: 130 tokens (3 pages) + 40 tokens (1 page)
+        reqs = {"a": tokens(130, 97, 10 + r), "b": tokens(40, 97, 20 + r)}
+        sa, sb = m.open(), m.open()
+        with pytest.raises(Exception):
+            m.open()   # no third slot
+        la = m.step([(sa, reqs["a"][:100]), (sb, reqs["b"][:7])], [range(100), range(7)])
+        lb = m.step([(sb, reqs["b"][7:]), (sa, reqs["a"][100:])], [range(33), range(30)])
+        seen_pages.append(sorted(m.pages(sa) + m.pages(sb)))
+        seen_slots.append((sa, sb))
+        with pytest.raises(Exception):
+            m.step([(sb, tokens(30, 97))], [[]])   # b would need a second page: the pool is exhausted, nothing changes
+        assert m.length(sb) == 40
+        got_a = np.concatenate([la[:100], lb[33:]])
+        got_b = np.concatenate([la[100:], lb[:33]])
+        assert rel_err(got_a, plain.forward(HYBRID, W, reqs["a"])) < TOL["float32"]
+        assert rel_err(got_b, plain.forward(HYBRID, W, reqs["b"])) < TOL["float32"]
+        m.close(sb)
+        m.close(sa)
+        assert m.pool_info()["free_pages"] == 4
+    assert all(p == [0, 1, 2, 3] for p in seen_pages)
+    m.free()
+
+
+# ---- faults that random weights would hide: one score stands out --------------------------------------------------------------
+def peaked(window, n, seed):
+    """One attention layer whose score scale is so large that the softmax is nearly one-hot: a key that is wrongly visible or
+    wrongly hidden changes the output completely."""
+    cfg = make_config([attn_layer(heads=2, kv_heads=1, dim=16, vdim=16, rot_dims=8, window=window, scale=3.0)], width=32)
+    return cfg, random_weights(cfg, seed=seed), tokens(n, cfg["vocab"], seed)
+
+
+@pytest.mark.parametrize("window,n", [(5, 40), (64, 200), (65, 200), (63, 200), (128, 300), (500, 700)])
+def test_window_edges_with_peaked_scores(window, n):
+    cfg, W, toks = peaked(window, n, 11)
+    want = plain.forward(cfg, W, toks)
+    # the plain implementation itself separates window - 1 / window / window + 1 on these inputs
+    for other in (window - 1, window + 1):
+        c2 = make_config([dict(cfg["layers"][0], mixer=dict(cfg["layers"][0]["mixer"], mask={"size": other}))], width=32)
+        assert rel_err(plain.forward(c2, W, toks), want) > 0.05
+    m = build_engine(cfg, W, "float32", max_tokens=1024)
+    a = whole(m, toks)
+    cut = n - min(n - 1, window + 10)   # the window passes over decoded tokens
+    b = run_schedule(m, {"a": toks}, [[("a", cut)]] + [[("a", 1)]] * (n - cut))["a"]
+    m.free()
+    assert rel_err(a, want) < 1e-3 and rel_err(b, want) < 1e-3
+
+
+def test_far_key_among_hundreds():
+    # key 3 is made to match the last query exactly (same token, no rotation), all others are random: attention must find it
+    cfg = make_config([attn_layer(heads=1, kv_heads=1, dim=16, vdim=16, rot_dims=0, window=900, scale=4.0)], width=32)
+    W = random_weights(cfg, seed=12)
+    W["l0.mix.k"] = W["l0.mix.q"].copy()
+    toks = tokens(800, cfg["vocab"], 12)
+    toks = [t if t != 5 else 6 for t in toks]
+    toks[3] = toks[-1] = 5
+    want = plain.forward(cfg, W, toks)
+    m = build_engine(cfg, W, "float32", max_tokens=1024)
+    a = whole(m, toks)
+    b = run_schedule(m, {"a": toks}, [[("a", 700)], [("a", 98)], [("a", 1)], [("a", 1)]])["a"]
+    m.free()
+    assert rel_err(a[-1:], want[-1:]) < 1e-3 and rel_err(b[-1:], want[-1:]) < 1e-3
+    assert rel_err(a, want) < 1e-3
+
+
+def test_recurrent_state_long_memory():
+    # decays close to 1: what the first tokens wrote into the state still matters hundreds of tokens later
+    cfg = make_config([wkv_layer(heads=2, dim=16)], width=32)
+    W = random_weights(cfg, seed=13, decay_bias=-7.0)
+    toks = tokens(400, cfg["vocab"], 13)
+    want = plain.forward(cfg, W, toks)
+    other = plain.forward(cfg, W, [(toks[0] + 1) % cfg["vocab"]] + toks[1:])
+    assert rel_err(other[-1:], want[-1:]) > 5e-3   # the plain implementation sees the first token at the end
+    m = build_engine(cfg, W, "float32", max_tokens=512)
+    a = whole(m, toks)
+    b = run_schedule(m, {"a": toks}, [[("a", 100)], [("a", 2)]] + [[("a", 1)]] * 298)["a"]
+    m.free()
+    assert rel_err(a, want) < TOL["float32"] and rel_err(b, want) < TOL["float32"]
+
+
+def test_first_tokens_and_single_token_requests():
+    W = random_weights(HYBRID, seed=14)
+    m = build_engine(HYBRID, W, "float32")
+    for n in (1, 2, 3):
+        toks = tokens(n, 97, 30 + n)
+        assert rel_err(whole(m, toks), plain.forward(HYBRID, W, toks)) < TOL["float32"]
+    m.free()
+
+
+def test_long_decoding():
+    cfg = make_config([wkv_layer(), attn_layer(window=48, ff=32)], loop=(0, 2, 2))
+    W = random_weights(cfg, seed=15)
+    toks = tokens(420, cfg["vocab"], 15)
+    want = plain.forward(cfg, W, toks)
+    m = build_engine(cfg, W, "float32", max_tokens=448)
+    got = run_schedule(m, {"a": toks}, [[("a", 20)]] + [[("a", 1)]] * 400)["a"]
+    m.free()
+    assert rel_err(got, want) < TOL["float32"]
+
+
+# ---- generation through the engine's own loop -------------------------------------------------------------------------------
+def plain_greedy(cfg, W, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(np.argmax(plain.forward(cfg, W, toks)[-1])))
+    return toks[len(prompt):]
+
+
+def test_greedy_generation_continuous_batching():
+    cfg = make_config([wkv_layer(), attn_layer(window=20, ff=48)], loop=(0, 2, 2), vocab=61)
+    W = random_weights(cfg, seed=16)
+    prompts = [tokens(n, 61, 40 + n) for n in (5, 70, 1, 33, 12, 64)]
+    want = [plain_greedy(cfg, W, p, 12) for p in prompts]
+    # 3 slots and a pool that cannot hold all six at once: requests wait, slots and pages are used again; portions of 16 rows
+    m = build_engine(cfg, W, "float32", max_tokens=320, max_seqs=3)
+    got = m.generate(prompts, 12, step_tokens=16)
+    assert got == want
+    assert m.pool_info()["free_pages"] == m.pool_info()["total_pages"] and m.pool_info()["free_slots"] == 3
+    # the same through single steps with on-device arg-max
+    s = m.open()
+    out, _ = m.step_sample([(s, prompts[1])])
+    seq = [int(out[0])]
+    for _ in range(11):
+        out, _ = m.step_sample([(s, [seq[-1]])])
+        seq.append(int(out[0]))
+    m.close(s)
+    m.free()
+    assert seq == want[1]
+
+
+def test_sampling_is_reproducible_and_respects_top_k():
+    cfg = make_config([attn_layer()], vocab=61)
+    W = random_weights(cfg, seed=17)
+    m = build_engine(cfg, W, "float32")
+    p = [tokens(10, 61, 50)]
+    a = m.generate(p, 16, temperature=0.9, top_k=5, top_p=0.95, seed=7)
+    b = m.generate(p, 16, temperature=0.9, top_k=5, top_p=0.95, seed=7)
+    c = m.generate(p, 16, temperature=0.9, top_k=5, top_p=0.95, seed=8)
+    assert a == b and a != c
+    # every pick is among the 5 most likely tokens of the plain implementation at its place
+    seq = list(p[0])
+    for t in a[0]:
+        top = np.argsort(-plain.forward(cfg, W, seq)[-1])[:5]
+        assert t in top
+        seq.append(t)
+    assert m.generate(p, 8, temperature=1.0, top_k=1) == m.generate(p, 8)
+    m.free()
+
+
+def test_eos_stops_a_request():
+    cfg = make_config([attn_layer()], vocab=61)
+    W = random_weights(cfg, seed=18)
+    m = build_engine(cfg, W, "float32")
+    p = [tokens(6, 61, 60)]
+    full = m.generate(p, 10)[0]
+    cut = m.generate(p, 10, eos=full[3])[0]
+    m.free()
+    assert cut == full[:full.index(full[3]) + 1]
+
+
+def test_errors_are_reported():
+    cfg = make_config([attn_layer()])
+    W = random_weights(cfg, seed=19)
+    bad = dict(W)
+    bad["l0.mix.q"] = W["l0.mix.q"][:-1]
+    with pytest.raises(Exception):
+        build_engine(cfg, bad)
+    missing = {k: v for k, v in W.items() if k != "head"}
+    with pytest.raises(Exception):
+        build_engine(cfg, missing)
+    m = build_engine(cfg, W)
+    s = m.open()
+    with pytest.raises(Exception):
+        m.step([(s, [cfg["vocab"]])], [[0]])   # token outside the vocabulary
+    with pytest.raises(Exception):
+        m.step([(s + 1, [1])], [[0]])          # a sequence that is not open
+    m.free()
