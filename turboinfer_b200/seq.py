@@ -163,8 +163,8 @@ class SeqModel:
         if isinstance(value, Bf16Array):
             data, shape, dt = value.bits, value.shape, BF16
         else:
-            data = np.ascontiguousarray(value, dtype=np.float32)
-            shape, dt = data.shape, F32
+            a = np.asarray(value, dtype=np.float32)
+            data, shape, dt = np.ascontiguousarray(a).reshape(-1), a.shape, F32   # (a 0-d array stays 0-d in `shape`)
         sh = (C.c_int64 * max(1, len(shape)))(*shape)
         _ck(lib().ti_seq_model_set_tensor(self.h, name.encode(), dt, data.ctypes.data_as(C.c_void_p), sh, len(shape)))
 
