@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "seq_kernels.cuh"
+#include "seq_gemm_tc.cuh"
 #include "sampling.cuh"
 
 using namespace tib;
@@ -29,6 +30,7 @@ int g_device = -1, g_num_sms = 0;
 cudaStream_t g_stream = nullptr;
 uint64_t g_launches = 0;
 size_t g_smem_optin = 0;
+bool g_use_tc = true;   // TURBOINFER_B200_SEQ_TC=0: prompt-side products stay on the warp-level tensor path (A/B measurements)
 
 int fail(const char* fmt, ...) {
     char buf[1024];
@@ -186,6 +188,9 @@ struct Model {
     int cap_rows = 0, cap_want = 0;
     DevBuf<float> x, x0, xc, h, proj, mixes, att, mo, act, lora, hn, logits, logprobs;
     DevBuf<int> meta, picks;
+    DevBuf<__nv_bfloat16> abf;   // bf16 copy of a product's activations for the tcgen05 path: [rows][max_k]
+    DevBuf<int> err;             // device flag: a bounded wait in a kernel ran out
+    int max_k = 0;
     int* meta_host = nullptr;
     size_t meta_host_cap = 0;
     int max_proj = 0, max_att = 0, max_ff = 0, max_rank = 0;
@@ -318,6 +323,28 @@ int concat_rows(Model& m, std::initializer_list<const Tensor*> parts, DevBuf<uin
     return 0;
 }
 
+// ---- tensor maps for the tcgen05 path: a bf16 matrix [rows][cols], cols contiguous, boxes of 64 x 128 with the 128-byte swizzle ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr));
+        if (!p || qr != cudaDriverEntryPointSuccess) return fail("cuTensorMapEncodeTiled is not available in this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)kTcBM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return 0;
+}
+
 // ---- matrix product dispatch ----------------------------------------------------------------------------------------------
 int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, int M, int N, int K, int epi = EPI_NONE, float alpha = 1.f) {
     if (M <= 0 || N <= 0) return 0;
@@ -329,6 +356,20 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
             gemv_rows_kernel<__nv_bfloat16><<<grid, warps * 32, xs_bytes, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha);
         else
             gemv_rows_kernel<float><<<grid, warps * 32, xs_bytes, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha);
+        LAUNCHED();
+        return 0;
+    }
+    // prompt-sized products in bf16 mode: tcgen05 (TMA wants 16-byte row pitches and bases)
+    if (m.d.mode == TI_SEQ_BF16 && g_use_tc && M > 32 && N >= 64 && K >= 64 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 && m.abf.p &&
+        (size_t)M * K <= m.abf.n) {
+        rows_to_bf16_kernel<<<grid_for((size_t)M * K / 4), 256, 0, g_stream>>>(A, lda, M, K, m.abf.p);
+        LAUNCHED();
+        CUtensorMap ma, mw;
+        TRY(make_tmap_bf16(&ma, m.abf.p, (uint64_t)K, (uint64_t)M));
+        TRY(make_tmap_bf16(&mw, W, (uint64_t)K, (uint64_t)N));
+        TcArgs g{};
+        g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.epi = epi; g.alpha = alpha; g.err = m.err.p;
+        gemm_bf16_tc_kernel<<<dim3((N + kTcBN - 1) / kTcBN, (M + kTcBM - 1) / kTcBM), kTcThreads, kTcSmemBytes, g_stream>>>(ma, mw, g);
         LAUNCHED();
         return 0;
     }
@@ -353,6 +394,7 @@ int ensure_scratch(Model& m, int rows, int want) {
         if (m.max_ff) TRY(m.act.alloc(R * (size_t)m.max_ff));
         if (m.max_rank) TRY(m.lora.alloc(R * (size_t)m.max_rank));
         if (m.dbg) TRY(m.dbg_buf.alloc(m.runs.size() * R * D));
+        if (m.d.mode == TI_SEQ_BF16 && g_use_tc) TRY(m.abf.alloc(R * (size_t)m.max_k));
         m.cap_rows = (int)R;
     }
     if (want > m.cap_want) {
@@ -561,7 +603,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     } else if (n_want > 0 && logits_host) {
         CK(cudaMemcpyAsync(logits_host, m.logits.p, (size_t)n_want * V * sizeof(float), cudaMemcpyDeviceToHost, g_stream));
     }
+    int kerr = 0;
+    CK(cudaMemcpyAsync(&kerr, m.err.p, sizeof(int), cudaMemcpyDeviceToHost, g_stream));
     CK(cudaStreamSynchronize(g_stream));
+    if (kerr) return fail("step: a bounded wait inside a kernel ran out (tensor-core product pipeline)");
     CK(cudaEventElapsedTime(&m.last_ms, m.ev0, m.ev1));
     for (int e = 0; e < E; ++e) m.seqs[seqs[e]].len += counts[e];
     return 0;
@@ -608,6 +653,8 @@ int ti_seq_init(int device) {
     if (!g_stream) CK(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes));
+    if (const char* e = getenv("TURBOINFER_B200_SEQ_TC")) g_use_tc = atoi(e) != 0;
     CK(cudaFuncSetAttribute(wkv_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
@@ -805,6 +852,9 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             CK(cudaMemset(R.prev.p, 0, R.prev.n * sizeof(float)));
         }
     }
+    m.max_k = std::max({2 * D, m.max_att, m.max_ff, m.max_rank, D});
+    TRY(m.err.alloc(1));
+    CK(cudaMemset(m.err.p, 0, sizeof(int)));
     CK(cudaEventCreate(&m.ev0));
     CK(cudaEventCreate(&m.ev1));
     m.finalized = true;

@@ -498,6 +498,21 @@ __global__ void gather_rows_kernel(const float* x, const int* rows, int D, float
     const int t = blockIdx.x;
     for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = x[(size_t)rows[t] * D + d];
 }
+// A[M][lda] (fp32) -> Y[M][K] (bf16, dense rows), four elements a thread; K a multiple of 4
+__global__ void rows_to_bf16_kernel(const float* A, int lda, int M, int K, __nv_bfloat16* y) {
+    const size_t n4 = (size_t)M * (K / 4);
+    const bool vec = (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (K / 4), c = (i % (K / 4)) * 4;
+        const float* src = A + r * lda + c;
+        float4 v;
+        if (vec) v = *reinterpret_cast<const float4*>(src);
+        else v = make_float4(src[0], src[1], src[2], src[3]);
+        __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(y + r * K + c);
+        d[0] = __floats2bfloat162_rn(v.x, v.y);
+        d[1] = __floats2bfloat162_rn(v.z, v.w);
+    }
+}
 __global__ void f32_to_bf16_kernel(const float* x, __nv_bfloat16* y, size_t n) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = __float2bfloat16_rn(x[i]);
 }
