@@ -30,6 +30,7 @@ MECHANISMS = {
     "attention_mqa_vdim": make_config([attn_layer(heads=3, kv_heads=1, dim=24, vdim=40, rot_dims=8, window=5)]),
     "attention_mha_window1": make_config([attn_layer(heads=2, kv_heads=2, window=1)]),
     "wkv": make_config([wkv_layer()]),
+    "wkv_state_in_registers": make_config([wkv_layer(heads=2, dim=32, rank=8), wkv_layer(heads=1, dim=64, rank=3), wkv_layer(heads=1, dim=128)], width=64),
     "wkv_wide_heads": make_config([wkv_layer(heads=3, dim=40, rank=7)], width=56),
     "feed_forward": make_config([attn_layer(ff=80), wkv_layer(ff=24)]),
     "loop": make_config([wkv_layer(), attn_layer(ff=64), attn_layer(window=7), wkv_layer()], loop=(1, 3, 3)),
@@ -68,7 +69,7 @@ def test_rotary_frequencies_bands():
 
 
 # ---- prompts against decoding, portions, batches -----------------------------------------------------------------------------
-HYBRID = make_config([wkv_layer(ff=40), attn_layer(window=24, ff=64), attn_layer(window=70, rot_dims=32, scaling=LLAMA3), wkv_layer()], loop=(0, 3, 2))
+HYBRID = make_config([wkv_layer(ff=40), attn_layer(window=24, ff=64), attn_layer(window=70, rot_dims=32, scaling=LLAMA3), wkv_layer(dim=32)], loop=(0, 3, 2))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -206,7 +207,7 @@ def test_first_tokens_and_single_token_requests():
 
 
 def test_long_decoding():
-    cfg = make_config([wkv_layer(), attn_layer(window=48, ff=32)], loop=(0, 2, 2))
+    cfg = make_config([wkv_layer(dim=32), attn_layer(window=48, ff=32)], loop=(0, 2, 2))
     W = random_weights(cfg, seed=15)
     toks = tokens(420, cfg["vocab"], 15)
     want = plain.forward(cfg, W, toks)

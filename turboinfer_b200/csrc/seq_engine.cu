@@ -30,6 +30,8 @@ int g_device = -1, g_num_sms = 0;
 cudaStream_t g_stream = nullptr;
 uint64_t g_launches = 0;
 size_t g_smem_optin = 0;
+bool g_use_tiled_attn = true;   // TURBOINFER_B200_SEQ_TILED_ATTN=0: every row goes through the row-at-a-time attention kernel
+constexpr int kAttnTiledMinRows = 8;   // portions at least this long are cut into attention tiles
 bool g_use_tc = true;   // TURBOINFER_B200_SEQ_TC=0: prompt-side products stay on the warp-level tensor path (A/B measurements)
 
 int fail(const char* fmt, ...) {
@@ -346,19 +348,33 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t r
 }
 
 // ---- matrix product dispatch ----------------------------------------------------------------------------------------------
-int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, int M, int N, int K, int epi = EPI_NONE, float alpha = 1.f) {
+// Fusion a caller may ask for; it happens inside the product when the step is a decode step (few rows) and the caller does the
+// separate kernel otherwise (gemm() says which through the return of fused()).
+struct Fuse {
+    const float* norm_gain = nullptr;   // scalar-gain RMS norm of the input rows in front of the product
+    float eps = 0.f;
+    int glu_ff = 0, glu_act = 0;        // act(gate) * up behind a fused [gate | up] product: N is then the inner size
+};
+bool few_rows(int M, int K) { return M <= kRowGemvMaxRows && (size_t)M * K * sizeof(float) <= g_smem_optin; }
+
+int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, int M, int N, int K, int epi = EPI_NONE, float alpha = 1.f,
+         const Fuse* fuse = nullptr) {
     if (M <= 0 || N <= 0) return 0;
     const size_t xs_bytes = (size_t)M * K * sizeof(float);
-    if (M <= kGemvMaxRows && xs_bytes <= g_smem_optin) {
-        const int warps = 8;
-        const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * 4));
+    if (few_rows(M, K)) {
+        const int warps = kRowGemvThreads / 32;
+        const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * 2));
+        const Fuse f = fuse ? *fuse : Fuse{};
         if (m.d.mode == TI_SEQ_BF16)
-            gemv_rows_kernel<__nv_bfloat16><<<grid, warps * 32, xs_bytes, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha);
+            gemv_rows_kernel<__nv_bfloat16><<<grid, kRowGemvThreads, xs_bytes, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain,
+                                                                                      f.eps, f.glu_ff, f.glu_act);
         else
-            gemv_rows_kernel<float><<<grid, warps * 32, xs_bytes, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha);
+            gemv_rows_kernel<float><<<grid, kRowGemvThreads, xs_bytes, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
+                                                                              f.glu_act);
         LAUNCHED();
         return 0;
     }
+    if (fuse) return fail("internal: a fused product was asked for on the many-row path");
     // prompt-sized products in bf16 mode: tcgen05 (TMA wants 16-byte row pitches and bases)
     if (m.d.mode == TI_SEQ_BF16 && g_use_tc && M > 32 && N >= 64 && K >= 64 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 && m.abf.p &&
         (size_t)M * K <= m.abf.n) {
@@ -455,7 +471,21 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     TRY(ensure_scratch(m, T, std::max(n_out, 1)));
     // meta buffer: tok | row_ent | row_pos | ent_row0 | ent_slot | ent_pos0 | out rows | page table
     const int stride = m.num_pages;
-    const size_t n_meta = (size_t)3 * T + (size_t)(E + 1) + 2 * (size_t)E + (size_t)std::max(n_out, 1) + (size_t)m.seqs.size() * stride;
+    // attention work lists: prompt portions are cut into tiles of up to 64 rows of one sequence, the other rows go one by one
+    std::vector<int> tiles, small_rows;
+    {
+        int r0 = 0;
+        for (int e = 0; e < E; ++e) {
+            if (counts[e] >= kAttnTiledMinRows)
+                for (int o = 0; o < counts[e]; o += kAttnTile) { tiles.push_back(r0 + o); tiles.push_back(std::min(kAttnTile, counts[e] - o)); }
+            else
+                for (int o = 0; o < counts[e]; ++o) small_rows.push_back(r0 + o);
+            r0 += counts[e];
+        }
+    }
+    const int n_tiles = (int)tiles.size() / 2, n_small = (int)small_rows.size();
+    const size_t n_meta = (size_t)3 * T + (size_t)(E + 1) + 2 * (size_t)E + (size_t)std::max(n_out, 1) + (size_t)m.seqs.size() * stride +
+                          (size_t)2 * T + 2;
     if (n_meta > m.meta_host_cap) {
         if (m.meta_host) cudaFreeHost(m.meta_host);
         m.meta_host = nullptr;
@@ -485,6 +515,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         for (int i = 0; i < n_want; ++i) h_out[i] = want_rows[i];
     for (size_t s = 0; s < m.seqs.size(); ++s)
         for (int p = 0; p < stride; ++p) h_table[s * stride + p] = p < (int)m.seqs[s].pages.size() ? m.seqs[s].pages[p] : 0;
+    int* h_tiles = h_table + m.seqs.size() * stride;
+    int* h_small = h_tiles + tiles.size();
+    std::copy(tiles.begin(), tiles.end(), h_tiles);
+    std::copy(small_rows.begin(), small_rows.end(), h_small);
     // the previous step's copy out of this pinned buffer has completed: every step ends with a stream synchronisation
     CK(cudaMemcpyAsync(m.meta.p, hp, n_meta * sizeof(int), cudaMemcpyHostToDevice, g_stream));
     StepMeta sm{};
@@ -496,6 +530,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     sm.ent_pos0 = sm.ent_slot + E;
     const int* d_out = sm.ent_pos0 + E;
     sm.page_table = d_out + std::max(n_out, 1);
+    const int* d_tiles = sm.page_table + m.seqs.size() * stride;
+    const int* d_small = d_tiles + tiles.size();
     sm.table_stride = stride;
     sm.T = T;
     sm.E = E;
@@ -515,19 +551,44 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             LAUNCHED();
             TRY(gemm(m, m.xc.p, 2 * D, m.loop_in, m.x.p, D, T, D, 2 * D));
         }
-        scalar_rmsnorm_kernel<<<T, nt, 0, g_stream>>>(m.x.p, nullptr, D, L.norm1, eps, m.h.p);
-        LAUNCHED();
-        if (L.d.mixer == TI_SEQ_MIXER_ATTENTION) {
+        // decode steps (few rows) fuse the norm in front of the attention projections into the product's prologue
+        const bool fuse_rows = few_rows(T, D);
+        const bool attn = L.d.mixer == TI_SEQ_MIXER_ATTENTION;
+        if (!(fuse_rows && attn)) {
+            scalar_rmsnorm_kernel<<<T, nt, 0, g_stream>>>(m.x.p, nullptr, D, L.norm1, eps, m.h.p);
+            LAUNCHED();
+        }
+        if (attn) {
             AttnShape s{};
             s.heads = L.d.heads; s.kv_heads = L.d.kv_heads; s.dim = L.d.dim; s.vdim = L.d.vdim;
             s.window = L.d.window; s.rot_dims = L.d.rot_dims; s.qk_norm = L.d.qk_norm; s.out_gate = L.d.out_gate;
             s.scale = L.d.scale; s.eps = eps; s.ld = L.n_qkvg;
-            TRY(gemm(m, m.h.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
+            if (fuse_rows) {
+                Fuse f;
+                f.norm_gain = L.norm1; f.eps = eps;
+                TRY(gemm(m, m.x.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D, EPI_NONE, 1.f, &f));
+            } else {
+                TRY(gemm(m, m.h.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
+            }
             attn_prepare_kernel<<<T, 128, 0, g_stream>>>(m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p);
             LAUNCHED();
             const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
-            window_attention_kernel<<<dim3(T, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, R.k_pool.p, R.v_pool.p, m.att.p);
-            LAUNCHED();
+            const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim);
+            const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && tsmem <= g_smem_optin;
+            if (tiled_ok) {
+                const dim3 grid(n_tiles, s.heads);
+                if (s.vdim <= 64) window_attention_tiled_kernel<1><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
+                else if (s.vdim <= 128) window_attention_tiled_kernel<2><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
+                else window_attention_tiled_kernel<4><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
+                LAUNCHED();
+                if (n_small > 0) {
+                    window_attention_kernel<<<dim3(n_small, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, d_small, R.k_pool.p, R.v_pool.p, m.att.p);
+                    LAUNCHED();
+                }
+            } else {
+                window_attention_kernel<<<dim3(T, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, nullptr, R.k_pool.p, R.v_pool.p, m.att.p);
+                LAUNCHED();
+            }
             TRY(gemm(m, m.att.p, s.heads * s.vdim, L.o, m.mo.p, D, T, D, s.heads * s.vdim));
         } else {
             const int C = L.d.heads * L.d.dim, d = L.d.dim, rank = L.d.decay_rank;
@@ -544,22 +605,36 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             TRY(gemm(m, m.mixes.p + 4 * TD, D, L.w1, m.lora.p, rank, T, rank, D, EPI_TANH));
             TRY(gemm(m, m.lora.p, rank, L.w2, pz, C, T, C, rank));
             WkvArgs a{};
-            a.r = pr; a.k = pk; a.v = pv; a.gate = pg; a.z = pz;
-            a.w0 = L.w0; a.u = L.u; a.normw = L.normw;
-            a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d; a.eps = eps;
-            const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
-            a.s_in_smem = full <= g_smem_optin ? 1 : 0;
-            wkv_scan_kernel<<<dim3(E, L.d.heads), (d + 31) / 32 * 32, a.s_in_smem ? full : small, g_stream>>>(a, sm);
+            a.r = pr; a.k = pk; a.v = pv; a.z = pz;
+            a.w0 = L.w0; a.u = L.u;
+            a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d;
+            const dim3 grid(E, L.d.heads);
+            if (d == 32) wkv_scan_reg_kernel<32><<<grid, 32, 0, g_stream>>>(a, sm);
+            else if (d == 64) wkv_scan_reg_kernel<64><<<grid, 64, 0, g_stream>>>(a, sm);
+            else if (d == 128) wkv_scan_reg_kernel<128><<<grid, 128, 0, g_stream>>>(a, sm);
+            else {
+                const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
+                a.s_in_smem = full <= g_smem_optin ? 1 : 0;
+                wkv_scan_kernel<<<grid, (d + 31) / 32 * 32, a.s_in_smem ? full : small, g_stream>>>(a, sm);
+            }
+            LAUNCHED();
+            wkv_finish_kernel<<<(T * L.d.heads + 7) / 8, 256, 0, g_stream>>>(m.att.p, pg, L.normw, T, L.d.heads, d, eps);
             LAUNCHED();
             TRY(gemm(m, m.att.p, C, L.o, m.mo.p, D, T, D, C));
         }
         if (L.d.ff > 0) {
-            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm1b, eps, L.norm2, m.h.p);
+            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm1b, eps, fuse_rows ? nullptr : L.norm2, m.h.p);
             LAUNCHED();
             const int F = L.d.ff;
-            TRY(gemm(m, m.h.p, D, L.gateup, m.proj.p, 2 * F, T, 2 * F, D));
-            glu_kernel<<<grid_for((size_t)T * F), 256, 0, g_stream>>>(m.proj.p, F, L.d.ff_act, m.act.p, (size_t)T * F);
-            LAUNCHED();
+            if (fuse_rows) {   // norm -> [gate | up] -> act(gate) * up in one launch
+                Fuse f;
+                f.norm_gain = L.norm2; f.eps = eps; f.glu_ff = F; f.glu_act = L.d.ff_act;
+                TRY(gemm(m, m.x.p, D, L.gateup, m.act.p, F, T, F, D, EPI_NONE, 1.f, &f));
+            } else {
+                TRY(gemm(m, m.h.p, D, L.gateup, m.proj.p, 2 * F, T, 2 * F, D));
+                glu_kernel<<<grid_for((size_t)T * F), 256, 0, g_stream>>>(m.proj.p, F, L.d.ff_act, m.act.p, (size_t)T * F);
+                LAUNCHED();
+            }
             TRY(gemm(m, m.act.p, F, L.down, m.mo.p, D, T, D, F));
             postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm2b, eps, nullptr, nullptr);
             LAUNCHED();
@@ -571,9 +646,17 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     }
     m.dbg_rows = T;
     if (n_out > 0) {
-        scalar_rmsnorm_kernel<<<n_out, nt, 0, g_stream>>>(m.x.p, d_out, D, m.final_norm, eps, m.hn.p);
-        LAUNCHED();
-        TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale));
+        if (few_rows(n_out, D)) {
+            gather_rows_kernel<<<n_out, nt, 0, g_stream>>>(m.x.p, d_out, D, m.hn.p);
+            LAUNCHED();
+            Fuse f;
+            f.norm_gain = m.final_norm; f.eps = eps;
+            TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale, &f));
+        } else {
+            scalar_rmsnorm_kernel<<<n_out, nt, 0, g_stream>>>(m.x.p, d_out, D, m.final_norm, eps, m.hn.p);
+            LAUNCHED();
+            TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale));
+        }
     }
     if (smp.on) {
         const bool greedy = !(smp.temperature > 0.f) || smp.top_k == 1;
@@ -655,6 +738,10 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(gemv_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes));
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TC")) g_use_tc = atoi(e) != 0;
+    if (const char* e = getenv("TURBOINFER_B200_SEQ_TILED_ATTN")) g_use_tiled_attn = atoi(e) != 0;
+    CK(cudaFuncSetAttribute(window_attention_tiled_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(window_attention_tiled_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(window_attention_tiled_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(wkv_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));

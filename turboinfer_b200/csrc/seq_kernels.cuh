@@ -236,33 +236,85 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const float* A, int lda,
             }
 }
 
-// few rows (M <= 8, the decode step): the weights are streamed once, one warp per output column; the rows sit in shared
-// memory (rounded to the weight type).  Bound by the weight bytes.
-constexpr int kGemvMaxRows = 8;
-template <typename WT>
-__global__ void __launch_bounds__(256) gemv_rows_kernel(const float* A, int lda, const WT* W, float* C, int ldc, int M, int N, int K, int epi,
-                                                         float alpha) {
-    extern __shared__ float xs[];   // [M][K]
-    for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = act_round<WT>(A[(size_t)(i / K) * lda + (i % K)]);
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
-        const WT* w = W + (size_t)n * K;
-        float acc[kGemvMaxRows];
+// few rows (M <= 8, the decode step): the weights are streamed once with 16-byte loads, one warp per output column; the rows
+// sit in shared memory.  Fused in front: the scalar-gain RMS norm of the rows (norm_gain != null).  Fused behind: an activation
+// or scale, or the gated feed-forward's act(gate) * up over the row pair (n, n + glu_ff) of the fused [gate | up] matrix.
+// Bound by the weight bytes.
+constexpr int kRowGemvMaxRows = 8;
+constexpr int kRowGemvThreads = 512;
+__device__ __forceinline__ float ff_act(float z, int act);
+template <typename WT> __device__ __forceinline__ void load8(const WT* p, float (&w)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&w)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&w)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int r = 0; r < kGemvMaxRows; ++r) acc[r] = 0.f;
+    for (int i = 0; i < 4; ++i) {
+        w[2 * i] = __uint_as_float(u[i] << 16);
+        w[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+    }
+}
+template <typename WT>
+__device__ __forceinline__ void gemv_row_dot(const WT* w, const float* xs, int M, int K, bool vec, int lane, float (&acc)[kRowGemvMaxRows]) {
+#pragma unroll
+    for (int r = 0; r < kRowGemvMaxRows; ++r) acc[r] = 0.f;
+    if (vec) {
+#pragma unroll 2
+        for (int k = lane * 8; k < K; k += 256) {
+            float wv[8];
+            load8<WT>(w + k, wv);
+#pragma unroll
+            for (int r = 0; r < kRowGemvMaxRows; ++r)
+                if (r < M) {
+                    const float4 a = *reinterpret_cast<const float4*>(xs + r * K + k), b = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
+                    acc[r] = fmaf(a.x, wv[0], fmaf(a.y, wv[1], fmaf(a.z, wv[2], fmaf(a.w, wv[3], acc[r]))));
+                    acc[r] = fmaf(b.x, wv[4], fmaf(b.y, wv[5], fmaf(b.z, wv[6], fmaf(b.w, wv[7], acc[r]))));
+                }
+        }
+    } else {
         for (int k = lane; k < K; k += 32) {
             const float wv = to_f32(w[k]);
 #pragma unroll
-            for (int r = 0; r < kGemvMaxRows; ++r)
+            for (int r = 0; r < kRowGemvMaxRows; ++r)
                 if (r < M) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
         }
+    }
 #pragma unroll
-        for (int r = 0; r < kGemvMaxRows; ++r)
-            if (r < M) {
-                const float s = warp_sum(acc[r]);
-                if (lane == 0) C[(size_t)r * ldc + n] = epi_apply(s, epi, alpha);
-            }
+    for (int r = 0; r < kRowGemvMaxRows; ++r)
+        if (r < M) acc[r] = warp_sum(acc[r]);
+}
+template <typename WT>
+__global__ void __launch_bounds__(kRowGemvThreads) gemv_rows_kernel(const float* A, int lda, const WT* W, float* C, int ldc, int M, int N, int K, int epi,
+                                                                  float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act) {
+    extern __shared__ __align__(16) float xs[];   // [M][K]
+    __shared__ float rsc[kRowGemvMaxRows];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = A[(size_t)(i / K) * lda + (i % K)];
+    __syncthreads();
+    if (norm_gain) {
+        if (warp < M) {
+            float ss = 0.f;
+            for (int k = lane; k < K; k += 32) ss += xs[warp * K + k] * xs[warp * K + k];
+            ss = warp_sum(ss);
+            if (lane == 0) rsc[warp] = norm_gain[0] / sqrtf(ss / (float)K + eps);
+        }
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = act_round<WT>(norm_gain ? xs[i] * rsc[i / K] : xs[i]);
+    __syncthreads();
+    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
+    float acc[kRowGemvMaxRows], acc2[kRowGemvMaxRows];
+    for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
+        gemv_row_dot<WT>(W + (size_t)n * K, xs, M, K, vec, lane, acc);
+        if (glu_ff > 0) gemv_row_dot<WT>(W + (size_t)(n + glu_ff) * K, xs, M, K, vec, lane, acc2);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < kRowGemvMaxRows; ++r)
+                if (r < M) C[(size_t)r * ldc + n] = glu_ff > 0 ? ff_act(acc[r], glu_act) * acc2[r] : epi_apply(acc[r], epi, alpha);
+        }
     }
 }
 
@@ -323,10 +375,10 @@ __global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const 
 // multiplied by sigmoid(gate) of its head.  out[t][h * dv ..].
 constexpr int kAttnWarps = 4;
 constexpr int kAttnMaxPerLane = 8;   // head sizes up to 256
-__global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const float* qkvg, StepMeta m, AttnShape s, const float* k_pool,
-                                                                            const float* v_pool, float* out) {
+__global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const float* qkvg, StepMeta m, AttnShape s, const int* rows,
+                                                                            const float* k_pool, const float* v_pool, float* out) {
     extern __shared__ float sm[];   // [kAttnWarps][dv] partial outputs, then [kAttnWarps] max, [kAttnWarps] sum
-    const int t = blockIdx.x, h = blockIdx.y;
+    const int t = rows ? rows[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = m.row_pos[t];
     const int slot = m.ent_slot[m.row_ent[t]];
@@ -396,11 +448,158 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const
     }
 }
 
+// The same attention for prompt portions: a block owns up to 64 consecutive rows of ONE sequence and one query head, walks the
+// key pages its rows can see (a page = a 64-key tile, fetched once per block), and does both products as register-tiled fp32
+// loops out of shared memory: S = Q K^T (4 x 4 scores a thread), masking and online softmax per row across the 16 threads that
+// share it, O += P V.  Head sizes must be multiples of 4; tiles[2 i] = first row, tiles[2 i + 1] = row count.
+constexpr int kAttnTile = 64;
+template <int DV4>   // float4 column groups of the output a thread owns: ceil(dv / 64)
+__global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float* qkvg, StepMeta m, AttnShape s, const int* tiles,
+                                                                      const float* k_pool, const float* v_pool, float* out) {
+    extern __shared__ __align__(16) float smt[];
+    const int d = s.dim, dv = s.vdim, ldq = d + 4, ldp = kAttnTile + 4;
+    float* Qs = smt;
+    float* Ks = Qs + kAttnTile * ldq;
+    float* Vs = Ks + kAttnTile * ldq;
+    float* Ps = Vs + kAttnTile * dv;
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int row0 = tiles[2 * blockIdx.x], n = tiles[2 * blockIdx.x + 1], h = blockIdx.y;
+    const int p0 = m.row_pos[row0];
+    const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[row0]] * m.table_stride;
+    const int g = h / (s.heads / s.kv_heads);
+    for (int i = tid; i < kAttnTile * d; i += 256) {
+        const int r = i / d, k = i % d;
+        Qs[r * ldq + k] = r < n ? qkvg[(size_t)(row0 + r) * s.ld + (size_t)h * d + k] : 0.f;
+    }
+    const int lo = (s.window > 0 && p0 - s.window + 1 > 0) ? p0 - s.window + 1 : 0, hi = p0 + n - 1;
+    float mrow[4], lrow[4], acc[4][DV4 * 4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        mrow[i] = -INFINITY;
+        lrow[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < DV4 * 4; ++j) acc[i][j] = 0.f;
+    }
+    const size_t kstride = (size_t)s.kv_heads * d, vstride = (size_t)s.kv_heads * dv;
+    for (int pg = lo / kPageTokens; pg <= hi / kPageTokens; ++pg) {
+        __syncthreads();
+        const size_t tok0 = (size_t)table[pg] * kPageTokens;
+        const float* kb = k_pool + tok0 * kstride + (size_t)g * d;
+        const float* vb = v_pool + tok0 * vstride + (size_t)g * dv;
+        for (int i = tid; i < kAttnTile * (d / 4); i += 256) {
+            const int c = i / (d / 4), k4 = (i % (d / 4)) * 4, key = pg * kPageTokens + c;
+            const float4 v = (key >= lo && key <= hi) ? *reinterpret_cast<const float4*>(kb + (size_t)c * kstride + k4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(&Ks[c * ldq + k4]) = v;
+        }
+        for (int i = tid; i < kAttnTile * (dv / 4); i += 256) {
+            const int c = i / (dv / 4), k4 = (i % (dv / 4)) * 4, key = pg * kPageTokens + c;
+            const float4 v = (key >= lo && key <= hi) ? *reinterpret_cast<const float4*>(vb + (size_t)c * vstride + k4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(&Vs[c * dv + k4]) = v;
+        }
+        __syncthreads();
+        float sc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+        for (int k = 0; k < d; k += 4) {
+            float4 qa[4], kk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qa[i] = *reinterpret_cast<const float4*>(&Qs[(ty + 16 * i) * ldq + k]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) kk[j] = *reinterpret_cast<const float4*>(&Ks[(tx + 16 * j) * ldq + k]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    sc[i][j] = fmaf(qa[i].x, kk[j].x, fmaf(qa[i].y, kk[j].y, fmaf(qa[i].z, kk[j].z, fmaf(qa[i].w, kk[j].w, sc[i][j]))));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = ty + 16 * i, pos = p0 + r;
+            bool ok[4];
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int key = pg * kPageTokens + tx + 16 * j;
+                ok[j] = r < n && key <= pos && (s.window <= 0 || key > pos - s.window);
+                sc[i][j] = ok[j] ? sc[i][j] * s.scale : -INFINITY;
+                tmax = fmaxf(tmax, sc[i][j]);
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, o));
+            const float nm = fmaxf(mrow[i], tmax);
+            const float corr = (nm == -INFINITY) ? 1.f : expf(mrow[i] - nm);
+            float psum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float pj = ok[j] ? expf(sc[i][j] - nm) : 0.f;
+                Ps[r * ldp + tx + 16 * j] = pj;
+                psum += pj;
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) psum += __shfl_xor_sync(0xFFFFFFFFu, psum, o);
+            lrow[i] = lrow[i] * corr + psum;
+            mrow[i] = nm;
+#pragma unroll
+            for (int j = 0; j < DV4 * 4; ++j) acc[i][j] *= corr;
+        }
+        __syncthreads();
+        for (int c = 0; c < kAttnTile; c += 4) {
+            float4 pr[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pr[i] = *reinterpret_cast<const float4*>(&Ps[(ty + 16 * i) * ldp + c]);
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+                for (int jj = 0; jj < DV4; ++jj) {
+                    const int col = tx * 4 + 64 * jj;
+                    if (col < dv) {
+                        const float4 v = *reinterpret_cast<const float4*>(&Vs[(c + cc) * dv + col]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float p = cc == 0 ? pr[i].x : cc == 1 ? pr[i].y : cc == 2 ? pr[i].z : pr[i].w;
+                            acc[i][jj * 4 + 0] = fmaf(p, v.x, acc[i][jj * 4 + 0]);
+                            acc[i][jj * 4 + 1] = fmaf(p, v.y, acc[i][jj * 4 + 1]);
+                            acc[i][jj * 4 + 2] = fmaf(p, v.z, acc[i][jj * 4 + 2]);
+                            acc[i][jj * 4 + 3] = fmaf(p, v.w, acc[i][jj * 4 + 3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty + 16 * i;
+        if (r >= n) continue;
+        const int t = row0 + r;
+        float gate = 1.f;
+        if (s.out_gate) {
+            const float z = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * d + (size_t)s.kv_heads * dv + h];
+            gate = 1.f / (1.f + expf(-z));
+        }
+        const float f = gate / lrow[i];
+#pragma unroll
+        for (int jj = 0; jj < DV4; ++jj) {
+            const int col = tx * 4 + 64 * jj;
+            if (col < dv) {
+                float* o = out + (size_t)t * (s.heads * dv) + (size_t)h * dv + col;
+                o[0] = acc[i][jj * 4 + 0] * f;
+                o[1] = acc[i][jj * 4 + 1] * f;
+                o[2] = acc[i][jj * 4 + 2] * f;
+                o[3] = acc[i][jj * 4 + 3] * f;
+            }
+        }
+    }
+}
+inline size_t attn_tiled_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t)2 * kAttnTile * (d + 4) + (size_t)kAttnTile * dv + (size_t)kAttnTile * (kAttnTile + 4)); }
+
 // ---- gated feed-forward: act(gate) * up over the fused projection output [gate | up] ------------------------------------
 enum { ACT_RELU = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };
 __device__ __forceinline__ float ff_act(float z, int act) {
-    if (act == ACT_RELU) return fmaxf(z, 0.f);
-    if (act == ACT_SILU) return z / (1.f + expf(-z));
+    if (act == 0 /*ACT_RELU*/) return fmaxf(z, 0.f);
+    if (act == 1 /*ACT_SILU*/) return z / (1.f + expf(-z));
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 __global__ void glu_kernel(const float* gu, int ff, int act, float* y, size_t n) {
@@ -433,21 +632,20 @@ __global__ void wkv_save_prev_kernel(const float* h, StepMeta m, int D, float* p
     for (int d = threadIdx.x; d < D; d += blockDim.x) prev_state[(size_t)m.ent_slot[e] * D + d] = h[(size_t)t * D + d];
 }
 // The recurrence of one (entry, head), token by token: thread j owns column j of the state S [d][d] (key channel i, value
-// channel j).  o_j = sum_i r_i (S_ij + u_i k_i v_j); S_ij <- w_i S_ij + k_i v_j with w = exp(-exp(z + w0)).  The head's o is
-// divided by its RMS, multiplied by the channel weights and the gate.  S lives in shared memory while the entry's rows run
-// and goes back to the slot at the end (in global memory directly when it does not fit).
+// channel j).  o_j = sum_i r_i (S_ij + u_i k_i v_j); S_ij <- w_i S_ij + k_i v_j with w = exp(-exp(z + w0)).  The raw o goes to
+// `out`; wkv_finish_kernel divides every head's o by its RMS and applies channel weights and gate (that reduction is
+// independent of the scan, so it stays out of the sequential loop).
 struct WkvArgs {
-    const float *r, *k, *v, *gate, *z;   // [T][H * d] each (gate already through its activation)
-    const float *w0, *u, *normw;          // [H * d]
+    const float *r, *k, *v, *z;           // [T][H * d] each
+    const float *w0, *u;                  // [H * d]
     float* state;                         // [slots][H][d][d]
-    float* out;                           // [T][H * d]
+    float* out;                           // [T][H * d] raw o
     int heads, dim;
-    float eps;
     int s_in_smem;
 };
+// any head size: S in shared memory while the entry's rows run (in global memory directly when it does not fit)
 __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
     extern __shared__ float sm[];
-    __shared__ float red[32];
     const int e = blockIdx.x, hd = blockIdx.y, d = a.dim, j = threadIdx.x;
     const int C = a.heads * d;
     float* rs = sm;            // r_i
@@ -475,22 +673,83 @@ __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
             us[j] = a.u[hd * d + j] * kv;
         }
         __syncthreads();
-        float acc = 0.f;
         if (j < d) {
+            float acc = 0.f;
             const float vj = a.v[base + j];
             for (int i = 0; i < d; ++i) {
                 const float s = S[i * d + j];
                 acc = fmaf(rs[i], fmaf(us[i], vj, s), acc);
                 S[i * d + j] = fmaf(ws[i], s, ks[i] * vj);
             }
+            a.out[base + j] = acc;
         }
-        const float ss = block_sum(j < d ? acc * acc : 0.f, red);
-        if (j < d) a.out[base + j] = acc / sqrtf(ss / (float)d + a.eps) * a.normw[hd * d + j] * a.gate[base + j];
     }
     if (a.s_in_smem && j < d) {
         __syncthreads();
         for (int i = 0; i < d; ++i) Sg[i * d + j] = S[i * d + j];
     }
+}
+// head sizes 32 / 64 / 128: the thread's state column lives in registers, the token's r / k / decay / u k vectors are
+// double-buffered in shared memory (one barrier per token) and the next token's operands are fetched while this one runs
+template <int D>
+__global__ void __launch_bounds__(D) wkv_scan_reg_kernel(WkvArgs a, StepMeta m) {
+    __shared__ __align__(16) float buf[2][4][D];
+    const int e = blockIdx.x, hd = blockIdx.y, j = threadIdx.x;
+    const int C = a.heads * D;
+    float* Sg = a.state + ((size_t)m.ent_slot[e] * a.heads + hd) * (size_t)D * D;
+    float S[D];
+    const bool fresh = (m.ent_pos0[e] == 0);
+#pragma unroll
+    for (int i = 0; i < D; ++i) S[i] = fresh ? 0.f : Sg[i * D + j];
+    const float w0 = a.w0[hd * D + j], u = a.u[hd * D + j];
+    const int t0 = m.ent_row0[e], t1 = m.ent_row0[e + 1];
+    size_t base = (size_t)t0 * C + (size_t)hd * D + j;
+    float nr = a.r[base], nk = a.k[base], nz = a.z[base], nv = a.v[base];
+    for (int t = t0; t < t1; ++t) {
+        float(*b)[D] = buf[(t - t0) & 1];
+        b[0][j] = nr;
+        b[1][j] = nk;
+        b[2][j] = expf(-expf(nz + w0));
+        b[3][j] = u * nk;
+        const float vj = nv;
+        const size_t obase = base;
+        if (t + 1 < t1) {
+            base += C;
+            nr = a.r[base]; nk = a.k[base]; nz = a.z[base]; nv = a.v[base];
+        }
+        __syncthreads();
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < D; i += 4) {
+            const float4 r4 = *reinterpret_cast<const float4*>(&b[0][i]);
+            const float4 k4 = *reinterpret_cast<const float4*>(&b[1][i]);
+            const float4 w4 = *reinterpret_cast<const float4*>(&b[2][i]);
+            const float4 u4 = *reinterpret_cast<const float4*>(&b[3][i]);
+            acc = fmaf(r4.x, fmaf(u4.x, vj, S[i]), acc);
+            S[i] = fmaf(w4.x, S[i], k4.x * vj);
+            acc = fmaf(r4.y, fmaf(u4.y, vj, S[i + 1]), acc);
+            S[i + 1] = fmaf(w4.y, S[i + 1], k4.y * vj);
+            acc = fmaf(r4.z, fmaf(u4.z, vj, S[i + 2]), acc);
+            S[i + 2] = fmaf(w4.z, S[i + 2], k4.z * vj);
+            acc = fmaf(r4.w, fmaf(u4.w, vj, S[i + 3]), acc);
+            S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * vj);
+        }
+        a.out[obase] = acc;
+    }
+#pragma unroll
+    for (int i = 0; i < D; ++i) Sg[i * D + j] = S[i];
+}
+// o[t, head] / rms(o[t, head]) * normw * gate, in place: one warp per (row, head)
+__global__ void wkv_finish_kernel(float* o, const float* gate, const float* normw, int T, int heads, int d, float eps) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T * heads) return;
+    const int hd = warp % heads;
+    const size_t base = (size_t)(warp / heads) * heads * d + (size_t)hd * d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) ss += o[base + i] * o[base + i];
+    ss = warp_sum(ss);
+    const float sc = 1.f / sqrtf(ss / (float)d + eps);
+    for (int i = lane; i < d; i += 32) o[base + i] = o[base + i] * sc * normw[hd * d + i] * gate[base + i];
 }
 
 // ---- helpers -----------------------------------------------------------------------------------------------------------
