@@ -277,9 +277,18 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the extra single-GPU workloads measured beside the headline at N = 1")
     ap.add_argument("--tp", action="store_true", help="(default for N > 1) the N ranks form ONE tensor-parallel group decoding one sequence (strong scaling)")
     ap.add_argument("--dp", action="store_true", help="N > 1: N data-parallel replicas instead (no data-path collective, weak scaling)")
+    ap.add_argument("--arch-compare", default=None, choices=["w1024", "w2048", "w4096"],
+                    help="instead of the headline workload: prompt and decode throughput of a Binusun-style model (layered sequence engine, bf16) "
+                         "next to the INT4 Llama-style decoder at equal width, depth and feed-forward size; random weights")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate depth (the number is then NOT a bench value)")
     args = ap.parse_args()
 
+    if args.arch_compare:
+        from turboinfer_b200 import bench_seq
+        res = bench_seq.compare(args.arch_compare, steps=max(1, args.steps), warmup=max(3, args.warmup))
+        print(json.dumps({"metric": "arch_compare_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": max(1, args.steps), "warmup": max(3, args.warmup),
+                          "dtype": "bf16 (Binusun) / int4 (Llama-style)", "data": "synthetic", "peaks": {"hbm_GBps": measured_peak_gbs()}, **res}))
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -103,6 +103,8 @@ int ti_seq_debug_layers(ti_seq_model_t m, int32_t enable);
 int ti_seq_debug_layers_read(ti_seq_model_t m, float* out, size_t cap_floats, int32_t* runs, int32_t* rows);
 /* CUDA-event time of the last step (device work only), ms */
 int ti_seq_last_step_ms(ti_seq_model_t m, float* ms);
+/* writes a buffer larger than L2 (benchmarks: cold caches between timed steps) */
+int ti_seq_flush_l2(void);
 /* bytes of weights one step streams (every matrix once) and bytes of cache + state per cached token / per sequence */
 int ti_seq_model_bytes(ti_seq_model_t m, double* weight_bytes, double* kv_bytes_per_token, double* state_bytes_per_seq);
 

@@ -85,6 +85,22 @@ def test_prefill_equals_token_by_token(dtype):
     assert rel_err(b, a) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dim,kv_heads", [(64, 1), (128, 2)])
+def test_tensor_core_attention_path(dim, kv_heads):
+    # bf16 mode, head sizes 64 / 128: prompt portions go through the split-half tensor-core attention (tiles of 128 rows),
+    # single tokens through the row kernel; windows cross tile and page borders
+    cfg = make_config([attn_layer(heads=2, kv_heads=kv_heads, dim=dim, vdim=dim, rot_dims=dim // 2, window=100, ff=64)], width=64)
+    W = random_weights(cfg, seed=21)
+    toks = tokens(330, cfg["vocab"], 21)
+    want = plain.forward(cfg, W, toks)
+    m = build_engine(cfg, W, "bfloat16")
+    a = whole(m, toks)
+    b = run_schedule(m, {"a": toks}, [[("a", 130)], [("a", 70)], [("a", 9)], [("a", 100)]] + [[("a", 1)]] * 21)["a"]
+    m.free()
+    assert rel_err(a, want) < TOL["bfloat16"] and rel_err(b, want) < TOL["bfloat16"]
+    assert rel_err(b, a) < 2e-2
+
+
 @pytest.mark.parametrize("sizes", [[2] * 40, [3, 61, 2, 64, 5, 65, 1, 63, 2], [64, 64, 64], [1, 127, 2, 2, 100], [129, 2, 33]])
 def test_portions(sizes):
     W = random_weights(HYBRID, seed=6)

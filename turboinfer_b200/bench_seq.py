@@ -1,0 +1,134 @@
+"""Throughput of a Binusun-style model on the layered sequence engine next to the library's closest existing model (the
+INT4 Llama-style decoder of the persistent decode kernel) at equal width, depth and feed-forward size; random weights.
+
+Used by `bench.py --arch-compare SIZE`.  Prompt throughput: one request's whole prompt in one step.  Decode throughput: single
+tokens of B live sequences per step.  Times are CUDA-event times of the device work (L2 flushed between timed prompt steps; a
+decode step streams more weight bytes than L2 holds at the larger sizes) and wall-clock times around the public call."""
+from __future__ import annotations
+
+import math
+import statistics
+import time
+
+import numpy as np
+
+from . import models, seq
+
+SIZES = {
+    # width, query heads x head size, kv heads, feed-forward, window; recurrence heads x size, decay rank
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, ff=2816, window=512, wkv_heads=16, wkv_dim=64, rank=32, vocab=32000),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=5632, window=1024, wkv_heads=32, wkv_dim=64, rank=64, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=11008, window=1024, wkv_heads=64, wkv_dim=64, rank=64, vocab=32000),
+}
+
+
+def config_for(size: str) -> dict:
+    z = SIZES[size]
+    attn = {"type": "attention", "mlp": {"kind": "dense", "ff": z["ff"]},
+            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": z["window"]},
+                      "rot": {"base": 10000.0, "dims": z["dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+                      "scale": 1.0 / math.sqrt(z["dim"])}}
+    wkv = {"type": "wkv", "mlp": None, "mixer": {"heads": z["wkv_heads"], "dim": z["wkv_dim"]}}
+    # wkv, attention, attention looped twice, then a closing wkv: 7 layer runs (4 attention + feed-forward, 3 recurrent)
+    return {"architecture": "Binusun", "layers": [wkv, attn, attn, wkv], "loop": {"start": 0, "stop": 3, "times": 2}, "norm": {"eps": 1e-5},
+            "logit_scale": 1.0, "vocab": z["vocab"], "width": z["width"]}
+
+
+def build_synthetic(cfg: dict, rank: int, dtype: str, max_tokens: int, max_seqs: int) -> seq.SeqModel:
+    mode = {"bfloat16": seq.BF16, "float32": seq.F32}[dtype]
+    shapes = {f"l{i}.mix.w1": (rank, cfg["width"]) for i, L in enumerate(cfg["layers"]) if L["type"] == "wkv"}
+    desc, layers = models.binusun_descs(cfg, mode, max_tokens, max_seqs, shapes)
+    m = seq.SeqModel(desc, layers)
+    for k, (name, shape) in enumerate(m.tensor_specs()):
+        leaf = name.split(".")[-1]
+        if len(shape) == 0:
+            amp, off = 0.25, 1.0
+        elif ".mu." in name:
+            amp, off = 0.5, 0.5
+        elif leaf == "w0":
+            amp, off = 1.0, -1.0
+        elif leaf == "norm":
+            amp, off = 0.5, 1.0
+        elif leaf == "u":
+            amp, off = 1.0, 0.0
+        elif name == "embed":
+            amp, off = 1.0, 0.0
+        else:
+            amp, off = math.sqrt(3.0 / shape[-1]), 0.0
+        m.set_tensor_synthetic(name, shape, 1000 + k, amp, off)
+    return m.finalize()
+
+
+def prompt(n: int, vocab: int, offset: int = 0):
+    return [int((7919 * i + 1 + offset) % vocab) for i in range(n)]
+
+
+def measure_seq(size: str, dtype: str, n_prompt: int, n_new: int, batch: int, steps: int, warmup: int) -> dict:
+    cfg = config_for(size)
+    m = build_synthetic(cfg, SIZES[size]["rank"], dtype, max_tokens=(n_prompt + n_new + 64) * max(batch, 1) + 64, max_seqs=max(batch, 1))
+    V = cfg["vocab"]
+    launches0 = seq.launch_count()
+    # prompt: whole prompt in one step, first token sampled on the device
+    pre_dev, pre_wall = [], []
+    for it in range(warmup + steps):
+        s = m.open()
+        seq.flush_l2()
+        t0 = time.perf_counter()
+        m.step_sample([(s, prompt(n_prompt, V))])
+        if it >= warmup:
+            pre_wall.append(time.perf_counter() - t0)
+            pre_dev.append(m.last_step_ms())
+        m.close(s)
+    # decode: `batch` live sequences, one token each per step
+    ss = [m.open() for _ in range(batch)]
+    toks, _ = m.step_sample([(s, prompt(64, V, b)) for b, s in enumerate(ss)])
+    dec_dev, dec_wall = [], []
+    for it in range(warmup + n_new):
+        t0 = time.perf_counter()
+        toks, _ = m.step_sample([(s, [int(toks[b])]) for b, s in enumerate(ss)])
+        if it >= warmup:
+            dec_wall.append(time.perf_counter() - t0)
+            dec_dev.append(m.last_step_ms())
+    by = m.bytes()
+    for s in ss:
+        m.close(s)
+    launches = seq.launch_count() - launches0
+    m.free()
+    pre_ms, dec_ms = statistics.median(pre_dev), statistics.median(dec_dev)
+    return {"prefill_tokens_per_s": n_prompt / (pre_ms * 1e-3), "prefill_ms": pre_ms, "prefill_e2e_tokens_per_s": n_prompt / statistics.median(pre_wall),
+            "decode_tokens_per_s": batch / (dec_ms * 1e-3), "decode_ms_per_step": dec_ms,
+            "decode_e2e_tokens_per_s": batch / statistics.median(dec_wall), "batch": batch, "weight_bytes": by["weights"],
+            "decode_weight_GBps": by["weights"] / (dec_ms * 1e-3) / 1e9, "gpu_launches": launches}
+
+
+def measure_llama(size: str, n_prompt: int, n_new: int, steps: int, warmup: int) -> dict:
+    from . import capi
+    z = SIZES[size]
+    capi.init(0)
+    meta = dict(vocab=z["vocab"], hidden=z["width"], layers=7, heads=z["heads"], inter=z["ff"])
+    m = capi.Model(meta, capi.Q_INT4, attn_mode=1, rope_mode=1, max_seq=n_prompt + n_new + 64)
+    m.load_synthetic()
+    pr = prompt(n_prompt, z["vocab"])
+    pre, dec, wall = [], [], []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        _, _, ms = m.generate_greedy(pr, n_new)
+        if it >= warmup:
+            wall.append(time.perf_counter() - t0)
+            dec.append(ms)
+            pre.append(m.last_prefill_ms())
+    wb, _ = m.step_bytes(n_prompt)
+    m.free()
+    pre_ms, dec_ms = statistics.median(pre), statistics.median(dec) / max(1, n_new - 1)
+    return {"prefill_tokens_per_s": n_prompt / (pre_ms * 1e-3), "prefill_ms": pre_ms, "decode_tokens_per_s": 1.0 / (dec_ms * 1e-3),
+            "decode_ms_per_step": dec_ms, "weight_bytes": wb, "decode_weight_GBps": wb / (dec_ms * 1e-3) / 1e9,
+            "e2e_s_per_generation": statistics.median(wall), "weights": "int4", "layers": 7}
+
+
+def compare(size: str, steps: int, warmup: int, n_prompt: int = 2048, n_new: int = 64, with_llama: bool = True) -> dict:
+    out = {"size": size, "shape": SIZES[size], "prompt_tokens": n_prompt, "decode_steps": n_new,
+           "binusun_bf16": measure_seq(size, "bfloat16", n_prompt, n_new, 1, steps, warmup),
+           "binusun_bf16_batch4": {k: v for k, v in measure_seq(size, "bfloat16", 256, n_new, 4, 1, 1).items() if k.startswith("decode") or k == "batch"}}
+    if with_llama:
+        out["llama_int4_same_width_depth"] = measure_llama(size, n_prompt, n_new, steps, warmup)
+    return out

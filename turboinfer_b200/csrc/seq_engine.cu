@@ -18,6 +18,7 @@
 
 #include "seq_kernels.cuh"
 #include "seq_gemm_tc.cuh"
+#include "seq_attn_tc.cuh"
 #include "sampling.cuh"
 
 using namespace tib;
@@ -31,7 +32,8 @@ cudaStream_t g_stream = nullptr;
 uint64_t g_launches = 0;
 size_t g_smem_optin = 0;
 bool g_use_tiled_attn = true;   // TURBOINFER_B200_SEQ_TILED_ATTN=0: every row goes through the row-at-a-time attention kernel
-constexpr int kAttnTiledMinRows = 8;   // portions at least this long are cut into attention tiles
+constexpr int kAttnTiledMinRows = 8;
+constexpr int kAttnMaxSplits = 16;    // key chunks of a decode row's attention   // portions at least this long are cut into attention tiles
 bool g_use_tc = true;   // TURBOINFER_B200_SEQ_TC=0: prompt-side products stay on the warp-level tensor path (A/B measurements)
 
 int fail(const char* fmt, ...) {
@@ -191,6 +193,8 @@ struct Model {
     DevBuf<float> x, x0, xc, h, proj, mixes, att, mo, act, lora, hn, logits, logprobs;
     DevBuf<int> meta, picks;
     DevBuf<__nv_bfloat16> abf;   // bf16 copy of a product's activations for the tcgen05 path: [rows][max_k]
+    DevBuf<float> attn_part;     // split-key attention partials: [rows][heads][splits][vdim + 2]
+    int max_heads_v = 0;         // max over attention layers of heads * (vdim + 2)
     DevBuf<int> err;             // device flag: a bounded wait in a kernel ran out
     int max_k = 0;
     int* meta_host = nullptr;
@@ -339,7 +343,7 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t r
     }
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)kTcBM};
+    const cuuint32_t box[2] = {(cuuint32_t)kSgBK, (cuuint32_t)kSgBM};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -385,7 +389,7 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
         TRY(make_tmap_bf16(&mw, W, (uint64_t)K, (uint64_t)N));
         TcArgs g{};
         g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.epi = epi; g.alpha = alpha; g.err = m.err.p;
-        gemm_bf16_tc_kernel<<<dim3((N + kTcBN - 1) / kTcBN, (M + kTcBM - 1) / kTcBM), kTcThreads, kTcSmemBytes, g_stream>>>(ma, mw, g);
+        gemm_bf16_tc_kernel<<<dim3((N + kSgBN - 1) / kSgBN, (M + kSgBM - 1) / kSgBM), kSgThreads, kSgSmemBytes, g_stream>>>(ma, mw, g);
         LAUNCHED();
         return 0;
     }
@@ -411,6 +415,7 @@ int ensure_scratch(Model& m, int rows, int want) {
         if (m.max_rank) TRY(m.lora.alloc(R * (size_t)m.max_rank));
         if (m.dbg) TRY(m.dbg_buf.alloc(m.runs.size() * R * D));
         if (m.d.mode == TI_SEQ_BF16 && g_use_tc) TRY(m.abf.alloc(R * (size_t)m.max_k));
+        if (m.max_heads_v) TRY(m.attn_part.alloc(R * (size_t)m.max_heads_v * kAttnMaxSplits));
         m.cap_rows = (int)R;
     }
     if (want > m.cap_want) {
@@ -472,20 +477,21 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     // meta buffer: tok | row_ent | row_pos | ent_row0 | ent_slot | ent_pos0 | out rows | page table
     const int stride = m.num_pages;
     // attention work lists: prompt portions are cut into tiles of up to 64 rows of one sequence, the other rows go one by one
-    std::vector<int> tiles, small_rows;
+    std::vector<int> tiles, tiles128, small_rows;
     {
         int r0 = 0;
         for (int e = 0; e < E; ++e) {
-            if (counts[e] >= kAttnTiledMinRows)
+            if (counts[e] >= kAttnTiledMinRows) {
                 for (int o = 0; o < counts[e]; o += kAttnTile) { tiles.push_back(r0 + o); tiles.push_back(std::min(kAttnTile, counts[e] - o)); }
-            else
+                for (int o = 0; o < counts[e]; o += kAttnTcTile) { tiles128.push_back(r0 + o); tiles128.push_back(std::min(kAttnTcTile, counts[e] - o)); }
+            } else
                 for (int o = 0; o < counts[e]; ++o) small_rows.push_back(r0 + o);
             r0 += counts[e];
         }
     }
-    const int n_tiles = (int)tiles.size() / 2, n_small = (int)small_rows.size();
+    const int n_tiles = (int)tiles.size() / 2, n_tiles128 = (int)tiles128.size() / 2, n_small = (int)small_rows.size();
     const size_t n_meta = (size_t)3 * T + (size_t)(E + 1) + 2 * (size_t)E + (size_t)std::max(n_out, 1) + (size_t)m.seqs.size() * stride +
-                          (size_t)2 * T + 2;
+                          (size_t)3 * T + 4;
     if (n_meta > m.meta_host_cap) {
         if (m.meta_host) cudaFreeHost(m.meta_host);
         m.meta_host = nullptr;
@@ -511,6 +517,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         if (smp.on) h_out[e] = row - 1;
     }
     h_row0[E] = row;
+    int max_pos = 0;
+    for (int e = 0; e < E; ++e) max_pos = std::max(max_pos, m.seqs[seqs[e]].len + counts[e] - 1);
     if (!smp.on)
         for (int i = 0; i < n_want; ++i) h_out[i] = want_rows[i];
     for (size_t s = 0; s < m.seqs.size(); ++s)
@@ -519,6 +527,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     int* h_small = h_tiles + tiles.size();
     std::copy(tiles.begin(), tiles.end(), h_tiles);
     std::copy(small_rows.begin(), small_rows.end(), h_small);
+    int* h_tiles128 = h_small + small_rows.size();
+    std::copy(tiles128.begin(), tiles128.end(), h_tiles128);
     // the previous step's copy out of this pinned buffer has completed: every step ends with a stream synchronisation
     CK(cudaMemcpyAsync(m.meta.p, hp, n_meta * sizeof(int), cudaMemcpyHostToDevice, g_stream));
     StepMeta sm{};
@@ -532,6 +542,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     sm.page_table = d_out + std::max(n_out, 1);
     const int* d_tiles = sm.page_table + m.seqs.size() * stride;
     const int* d_small = d_tiles + tiles.size();
+    const int* d_tiles128 = d_small + small_rows.size();
     sm.table_stride = stride;
     sm.T = T;
     sm.E = E;
@@ -575,19 +586,38 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
             const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim);
             const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && tsmem <= g_smem_optin;
-            if (tiled_ok) {
+            // bf16 mode, head sizes 64 / 128: the split-half tensor-core kernel (fp32-accurate); fp32 mode keeps true fp32 arithmetic
+            const bool h3_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles128 > 0 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
+                               (s.kv_heads * s.dim) % 4 == 0;
+            const int* rest = (tiled_ok || h3_ok) ? d_small : nullptr;
+            const int n_rest = (tiled_ok || h3_ok) ? n_small : T;
+            if (h3_ok) {
+                const dim3 grid(n_tiles128, s.heads);
+                if (s.dim == 64) window_attention_h3_kernel<64><<<grid, kTcThreads, attn_h3_smem_bytes<64>(), g_stream>>>(m.proj.p, sm, s, d_tiles128, R.k_pool.p, R.v_pool.p, m.att.p);
+                else window_attention_h3_kernel<128><<<grid, kTcThreads, attn_h3_smem_bytes<128>(), g_stream>>>(m.proj.p, sm, s, d_tiles128, R.k_pool.p, R.v_pool.p, m.att.p);
+                LAUNCHED();
+            } else if (tiled_ok) {
                 const dim3 grid(n_tiles, s.heads);
                 if (s.vdim <= 64) window_attention_tiled_kernel<1><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
                 else if (s.vdim <= 128) window_attention_tiled_kernel<2><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
                 else window_attention_tiled_kernel<4><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
                 LAUNCHED();
-                if (n_small > 0) {
-                    window_attention_kernel<<<dim3(n_small, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, d_small, R.k_pool.p, R.v_pool.p, m.att.p);
+            }
+            if (n_rest > 0) {
+                // single rows: key chunks in parallel when the visible span is long and the rows alone would not fill the GPU
+                const int span = s.window > 0 ? std::min(s.window, max_pos + 1) : max_pos + 1;
+                int splits = 1;
+                if (span >= 256) splits = std::max(1, std::min({span / 64, kAttnMaxSplits, (2 * g_num_sms) / std::max(1, n_rest * s.heads)}));
+                if (splits > 1 && m.attn_part.p) {
+                    window_attention_split_kernel<<<dim3(n_rest, s.heads, splits), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, rest, splits, R.k_pool.p,
+                                                                                                                        R.v_pool.p, m.attn_part.p);
+                    LAUNCHED();
+                    attention_merge_kernel<<<(n_rest * s.heads + 7) / 8, 256, 0, g_stream>>>(m.attn_part.p, m.proj.p, sm, s, rest, n_rest, splits, m.att.p);
+                    LAUNCHED();
+                } else {
+                    window_attention_kernel<<<dim3(n_rest, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, rest, R.k_pool.p, R.v_pool.p, m.att.p);
                     LAUNCHED();
                 }
-            } else {
-                window_attention_kernel<<<dim3(T, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, nullptr, R.k_pool.p, R.v_pool.p, m.att.p);
-                LAUNCHED();
             }
             TRY(gemm(m, m.att.p, s.heads * s.vdim, L.o, m.mo.p, D, T, D, s.heads * s.vdim));
         } else {
@@ -609,9 +639,9 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.w0 = L.w0; a.u = L.u;
             a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d;
             const dim3 grid(E, L.d.heads);
-            if (d == 32) wkv_scan_reg_kernel<32><<<grid, 32, 0, g_stream>>>(a, sm);
-            else if (d == 64) wkv_scan_reg_kernel<64><<<grid, 64, 0, g_stream>>>(a, sm);
-            else if (d == 128) wkv_scan_reg_kernel<128><<<grid, 128, 0, g_stream>>>(a, sm);
+            if (d == 32) wkv_scan_reg_kernel<32><<<dim3(E, L.d.heads, 1), 32, 0, g_stream>>>(a, sm);
+            else if (d == 64) wkv_scan_reg_kernel<64><<<dim3(E, L.d.heads, 2), 32, 0, g_stream>>>(a, sm);
+            else if (d == 128) wkv_scan_reg_kernel<128><<<dim3(E, L.d.heads, 4), 32, 0, g_stream>>>(a, sm);
             else {
                 const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
                 a.s_in_smem = full <= g_smem_optin ? 1 : 0;
@@ -736,9 +766,11 @@ int ti_seq_init(int device) {
     if (!g_stream) CK(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
-    CK(cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes));
+    CK(cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgSmemBytes));
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TC")) g_use_tc = atoi(e) != 0;
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TILED_ATTN")) g_use_tiled_attn = atoi(e) != 0;
+    CK(cudaFuncSetAttribute(window_attention_h3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_h3_smem_bytes<64>()));
+    CK(cudaFuncSetAttribute(window_attention_h3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_h3_smem_bytes<128>()));
     CK(cudaFuncSetAttribute(window_attention_tiled_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(window_attention_tiled_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(window_attention_tiled_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
@@ -896,6 +928,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             if (!f.empty()) CK(cudaMemcpy(L.inv_freq.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
             m.max_proj = std::max(m.max_proj, L.n_qkvg);
             m.max_att = std::max(m.max_att, L.d.heads * L.d.vdim);
+            m.max_heads_v = std::max(m.max_heads_v, L.d.heads * (L.d.vdim + 2));
         } else {
             const int C = L.d.heads * L.d.dim;
             L.r = P(p + "mix.r"); L.k = P(p + "mix.k"); L.v = P(p + "mix.v"); L.g = P(p + "mix.g");
@@ -1110,6 +1143,15 @@ int ti_seq_debug_layers_read(ti_seq_model_t h, float* out, size_t cap_floats, in
     CK(cudaMemcpy(out, m->dbg_buf.p, n * sizeof(float), cudaMemcpyDeviceToHost));
     *runs = (int32_t)m->runs.size();
     *rows = m->dbg_rows;
+    return 0;
+}
+int ti_seq_flush_l2(void) {
+    static DevBuf<uint8_t> buf;
+    const size_t bytes = (size_t)256 << 20;
+    if (g_device < 0) return fail("ti_seq: not initialised");
+    TRY(buf.ensure(bytes));
+    CK(cudaMemsetAsync(buf.p, 1, bytes, g_stream));
+    CK(cudaStreamSynchronize(g_stream));
     return 0;
 }
 int ti_seq_last_step_ms(ti_seq_model_t h, float* ms) {

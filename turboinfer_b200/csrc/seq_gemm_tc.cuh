@@ -17,12 +17,12 @@
 namespace tib {
 namespace seq {
 
-constexpr int kTcBM = 128, kTcBN = 128, kTcBK = 64;      // BK in bf16 elements (128 bytes)
-constexpr int kTcStages = 3;
-constexpr int kTcThreads = 192;
-constexpr int kTcTileBytes = kTcBM * kTcBK * 2;          // 16 KiB
-constexpr int kTcStageBytes = 2 * kTcTileBytes;
-constexpr size_t kTcSmemBytes = (size_t)kTcStages * kTcStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kSgBM = 128, kSgBN = 128, kSgBK = 64;      // BK in bf16 elements (128 bytes)
+constexpr int kSgStages = 3;
+constexpr int kSgThreads = 192;
+constexpr int kSgTileBytes = kSgBM * kSgBK * 2;          // 16 KiB
+constexpr int kSgStageBytes = 2 * kSgTileBytes;
+constexpr size_t kSgSmemBytes = (size_t)kSgStages * kSgStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 
 struct TcArgs {
     int M, N, K;
@@ -57,26 +57,26 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(kTcThreads, 2)
+__global__ void __launch_bounds__(kSgThreads, 2)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const TcArgs g) {
     extern __shared__ uint8_t tsm_raw[];
     const uint32_t base = (smem_u32(tsm_raw) + 1023u) & ~1023u;
     uint8_t* tiles = tsm_raw + (base - smem_u32(tsm_raw));
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)kTcStages * kTcStageBytes);
-    uint64_t* empty = full + kTcStages;
-    uint64_t* tmem_full = empty + kTcStages;
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)kSgStages * kSgStageBytes);
+    uint64_t* empty = full + kSgStages;
+    uint64_t* tmem_full = empty + kSgStages;
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_full + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = blockIdx.x, mb = blockIdx.y;
-    const int KB = (g.K + kTcBK - 1) / kTcBK;
+    const int KB = (g.K + kSgBK - 1) / kSgBK;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kTcStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < kSgStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
         mbar_init(tmem_full, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr)), "n"(kTcBN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr)), "n"(kSgBN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -87,28 +87,28 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < KB; ++kb) {
-                const int st = kb % kTcStages, use = kb / kTcStages;
+                const int st = kb % kSgStages, use = kb / kSgStages;
                 if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1, g.err)) break;
-                mbar_arrive_expect_tx(&full[st], kTcStageBytes);
-                uint8_t* sbase = tiles + (size_t)st * kTcStageBytes;
-                tma_load_2d(sbase, &map_a, kb * kTcBK, mb * kTcBM, &full[st]);
-                tma_load_2d(sbase + kTcTileBytes, &map_w, kb * kTcBK, nb * kTcBN, &full[st]);
+                mbar_arrive_expect_tx(&full[st], kSgStageBytes);
+                uint8_t* sbase = tiles + (size_t)st * kSgStageBytes;
+                tma_load_2d(sbase, &map_a, kb * kSgBK, mb * kSgBM, &full[st]);
+                tma_load_2d(sbase + kSgTileBytes, &map_w, kb * kSgBK, nb * kSgBN, &full[st]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(kTcBM, kTcBN);
+            constexpr uint32_t idesc = umma_idesc_bf16(kSgBM, kSgBN);
             bool ok = true;
             for (int kb = 0; kb < KB && ok; ++kb) {
-                const int st = kb % kTcStages, use = kb / kTcStages;
+                const int st = kb % kSgStages, use = kb / kSgStages;
                 ok = mbar_wait_bounded(&full[st], use & 1, g.err);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sbase = base + st * kTcStageBytes;
+                const uint32_t sbase = base + st * kSgStageBytes;
 #pragma unroll
-                for (int k4 = 0; k4 < kTcBK / 16; ++k4) {
+                for (int k4 = 0; k4 < kSgBK / 16; ++k4) {
                     const uint64_t adesc = umma_desc_sw128(sbase + k4 * 32);
-                    const uint64_t bdesc = umma_desc_sw128(sbase + kTcTileBytes + k4 * 32);
+                    const uint64_t bdesc = umma_desc_sw128(sbase + kSgTileBytes + k4 * 32);
                     tc_mma_bf16(tmem, adesc, bdesc, idesc, (kb | k4) != 0 ? 1u : 0u);
                 }
                 tc_commit(&empty[st]);
@@ -119,9 +119,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool ok = mbar_wait_bounded(tmem_full, 0, g.err);
         tc_fence_after();
         const int q = warp & 3;
-        const int row = mb * kTcBM + q * 32 + lane;
+        const int row = mb * kSgBM + q * 32 + lane;
         const bool row_ok = ok && row < g.M && *reinterpret_cast<volatile int*>(g.err) == 0;
-        for (int c0 = 0; c0 < kTcBN; c0 += 16) {
+        for (int c0 = 0; c0 < kSgBN; c0 += 16) {
             uint32_t a[16];
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
             asm volatile(
@@ -131,7 +131,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 : "r"(taddr));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if (row_ok) {
-                const int nbase = nb * kTcBN + c0;
+                const int nbase = nb * kSgBN + c0;
                 float* crow = g.C + (size_t)row * g.ldc;
                 if ((g.ldc & 3) == 0 && nbase + 16 <= g.N && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0) {
 #pragma unroll
@@ -152,7 +152,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTcBN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kSgBN) : "memory");
     }
 }
 

@@ -689,52 +689,75 @@ __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
         for (int i = 0; i < d; ++i) Sg[i * d + j] = S[i * d + j];
     }
 }
-// head sizes 32 / 64 / 128: the thread's state column lives in registers, the token's r / k / decay / u k vectors are
-// double-buffered in shared memory (one barrier per token) and the next token's operands are fetched while this one runs
+// head sizes 32 / 64 / 128: a WARP owns 32 value columns of a head (grid z = column group), each lane keeps its column of the
+// state in registers; the token's r / k / decay / u k vectors are double-buffered in shared memory behind a warp barrier and the
+// next token's operands are fetched while this one runs.  Four partial sums break the dependency chain of the output.
 template <int D>
-__global__ void __launch_bounds__(D) wkv_scan_reg_kernel(WkvArgs a, StepMeta m) {
+__global__ void __launch_bounds__(32) wkv_scan_reg_kernel(WkvArgs a, StepMeta m) {
+    constexpr int PER = D / 32;   // elements of each token vector a lane fetches
     __shared__ __align__(16) float buf[2][4][D];
-    const int e = blockIdx.x, hd = blockIdx.y, j = threadIdx.x;
+    const int e = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane;
     const int C = a.heads * D;
     float* Sg = a.state + ((size_t)m.ent_slot[e] * a.heads + hd) * (size_t)D * D;
     float S[D];
     const bool fresh = (m.ent_pos0[e] == 0);
 #pragma unroll
     for (int i = 0; i < D; ++i) S[i] = fresh ? 0.f : Sg[i * D + j];
-    const float w0 = a.w0[hd * D + j], u = a.u[hd * D + j];
+    float w0[PER], u[PER], nr[PER], nk[PER], nz[PER];
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        w0[p] = a.w0[hd * D + lane + 32 * p];
+        u[p] = a.u[hd * D + lane + 32 * p];
+    }
     const int t0 = m.ent_row0[e], t1 = m.ent_row0[e + 1];
-    size_t base = (size_t)t0 * C + (size_t)hd * D + j;
-    float nr = a.r[base], nk = a.k[base], nz = a.z[base], nv = a.v[base];
+    size_t base = (size_t)t0 * C + (size_t)hd * D;
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        nr[p] = a.r[base + lane + 32 * p];
+        nk[p] = a.k[base + lane + 32 * p];
+        nz[p] = a.z[base + lane + 32 * p];
+    }
+    float nv = a.v[base + j];
     for (int t = t0; t < t1; ++t) {
         float(*b)[D] = buf[(t - t0) & 1];
-        b[0][j] = nr;
-        b[1][j] = nk;
-        b[2][j] = expf(-expf(nz + w0));
-        b[3][j] = u * nk;
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+            b[0][lane + 32 * p] = nr[p];
+            b[1][lane + 32 * p] = nk[p];
+            b[2][lane + 32 * p] = expf(-expf(nz[p] + w0[p]));
+            b[3][lane + 32 * p] = u[p] * nk[p];
+        }
         const float vj = nv;
         const size_t obase = base;
         if (t + 1 < t1) {
             base += C;
-            nr = a.r[base]; nk = a.k[base]; nz = a.z[base]; nv = a.v[base];
+#pragma unroll
+            for (int p = 0; p < PER; ++p) {
+                nr[p] = a.r[base + lane + 32 * p];
+                nk[p] = a.k[base + lane + 32 * p];
+                nz[p] = a.z[base + lane + 32 * p];
+            }
+            nv = a.v[base + j];
         }
-        __syncthreads();
-        float acc = 0.f;
+        __syncwarp();
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
         for (int i = 0; i < D; i += 4) {
             const float4 r4 = *reinterpret_cast<const float4*>(&b[0][i]);
             const float4 k4 = *reinterpret_cast<const float4*>(&b[1][i]);
             const float4 w4 = *reinterpret_cast<const float4*>(&b[2][i]);
             const float4 u4 = *reinterpret_cast<const float4*>(&b[3][i]);
-            acc = fmaf(r4.x, fmaf(u4.x, vj, S[i]), acc);
+            acc0 = fmaf(r4.x, fmaf(u4.x, vj, S[i]), acc0);
             S[i] = fmaf(w4.x, S[i], k4.x * vj);
-            acc = fmaf(r4.y, fmaf(u4.y, vj, S[i + 1]), acc);
+            acc1 = fmaf(r4.y, fmaf(u4.y, vj, S[i + 1]), acc1);
             S[i + 1] = fmaf(w4.y, S[i + 1], k4.y * vj);
-            acc = fmaf(r4.z, fmaf(u4.z, vj, S[i + 2]), acc);
+            acc2 = fmaf(r4.z, fmaf(u4.z, vj, S[i + 2]), acc2);
             S[i + 2] = fmaf(w4.z, S[i + 2], k4.z * vj);
-            acc = fmaf(r4.w, fmaf(u4.w, vj, S[i + 3]), acc);
+            acc3 = fmaf(r4.w, fmaf(u4.w, vj, S[i + 3]), acc3);
             S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * vj);
         }
-        a.out[obase] = acc;
+        a.out[obase + j] = (acc0 + acc1) + (acc2 + acc3);
+        // the buffer written two tokens from now is this one: every lane has read it by the warp barrier of the next token
     }
 #pragma unroll
     for (int i = 0; i < D; ++i) Sg[i * D + j] = S[i];

@@ -59,6 +59,7 @@ SYMBOLS = {
                                   C.c_int32, _i32, _i32]),
     "ti_seq_debug_layers": (C.c_int, [C.c_uint64, C.c_int32]),
     "ti_seq_debug_layers_read": (C.c_int, [C.c_uint64, _f, C.c_size_t, _i32, _i32]),
+    "ti_seq_flush_l2": (C.c_int, []),
     "ti_seq_last_step_ms": (C.c_int, [C.c_uint64, _f]),
     "ti_seq_model_bytes": (C.c_int, [C.c_uint64, _d, _d, _d]),
 }
@@ -100,6 +101,10 @@ def init(device: int = 0) -> None:
     if not _inited:
         _ck(lib().ti_seq_init(device))
         _inited = True
+
+
+def flush_l2() -> None:
+    _ck(lib().ti_seq_flush_l2())
 
 
 def launch_count() -> int:
