@@ -197,26 +197,43 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
     const int j0 = lo + z * chunk, j1 = min(pos, j0 + chunk - 1);
     float mx = -INFINITY, l = 0.f;
     const size_t kstride = (size_t)s.kv_heads * s.dim, vstride = (size_t)s.kv_heads * s.vdim;
-    for (int j = j0 + warp; j <= j1; j += kAttnWarps) {
-        const size_t off = (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens;
-        const float* kr = k_pool + off * kstride + (size_t)g * s.dim;
-        float sc = 0.f;
+    // a warp takes its keys four at a time: the four K rows (and then the four V rows) are requested together
+    for (int jb = j0 + 4 * warp; jb <= j1; jb += 4 * kAttnWarps) {
+        size_t off[4];
+        float sc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = min(jb + u, j1);
+            off[u] = (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens;
+            sc[u] = 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < kAttnMaxPerLane; ++i) {
             const int d = lane + 32 * i;
-            if (d < s.dim) sc = fmaf(qr[i], kr[d], sc);
+            if (d < s.dim) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) sc[u] = fmaf(qr[i], k_pool[off[u] * kstride + (size_t)g * s.dim + d], sc[u]);
+            }
         }
-        sc = warp_sum(sc) * s.scale;
-        const float nm = fmaxf(mx, sc);
-        const float corr = expf(mx - nm), p = expf(sc - nm);
-        l = l * corr + p;
-        const float* vr = v_pool + off * vstride + (size_t)g * s.vdim;
+        float vv[4][kAttnMaxPerLane];
 #pragma unroll
         for (int i = 0; i < kAttnMaxPerLane; ++i) {
             const int d = lane + 32 * i;
-            if (d < s.vdim) o[i] = fmaf(p, vr[d], o[i] * corr);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) vv[u][i] = d < s.vdim ? v_pool[off[u] * vstride + (size_t)g * s.vdim + d] : 0.f;
         }
-        mx = nm;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float su = warp_sum(sc[u]) * s.scale;
+            if (jb + u <= j1) {
+                const float nm = fmaxf(mx, su);
+                const float corr = expf(mx - nm), p = expf(su - nm);
+                l = l * corr + p;
+#pragma unroll
+                for (int i = 0; i < kAttnMaxPerLane; ++i) o[i] = fmaf(p, vv[u][i], o[i] * corr);
+                mx = nm;
+            }
+        }
     }
     float* po = sm;
     float* pm = sm + kAttnWarps * s.vdim;
@@ -249,31 +266,31 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
         dst[1] = L;
     }
 }
-// one warp per (row, head): combines the splits in split order, divides by the sum, applies the gate
+// one warp per (row, head): lane z holds split z's (max, sum); the output coordinates are spread over the lanes
 __global__ void attention_merge_kernel(const float* part, const float* qkvg, StepMeta m, AttnShape s, const int* rows, int n_rows, int splits, float* out) {
     const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (wid >= n_rows * s.heads) return;
     const int bx = wid / s.heads, h = wid % s.heads, t = rows ? rows[bx] : bx;
-    const float* p = part + ((size_t)bx * s.heads + h) * splits * (size_t)(s.vdim + 2);
-    float Mx = -INFINITY;
-    for (int z = 0; z < splits; ++z) Mx = fmaxf(Mx, p[(size_t)z * (s.vdim + 2)]);
-    float L = 0.f;
-    for (int z = 0; z < splits; ++z) {
-        const float mz = p[(size_t)z * (s.vdim + 2)];
-        if (mz != -INFINITY) L += p[(size_t)z * (s.vdim + 2) + 1] * expf(mz - Mx);
-    }
+    const size_t ps = (size_t)(s.vdim + 2);
+    const float* p = part + ((size_t)bx * s.heads + h) * splits * ps;
+    const float mz = lane < splits ? p[(size_t)lane * ps] : -INFINITY;
+    const float lz = lane < splits ? p[(size_t)lane * ps + 1] : 0.f;
+    const float Mx = warp_max(mz);
+    const float fz = mz == -INFINITY ? 0.f : expf(mz - Mx);
+    const float L = warp_sum(lz * fz);
     float gate = 1.f;
     if (s.out_gate) {
         const float zg = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * s.dim + (size_t)s.kv_heads * s.vdim + h];
         gate = 1.f / (1.f + expf(-zg));
     }
-    for (int d = lane; d < s.vdim; d += 32) {
+    for (int d0 = 0; d0 < s.vdim; d0 += 32) {
+        const int d = d0 + lane;
         float acc = 0.f;
         for (int z = 0; z < splits; ++z) {
-            const float mz = p[(size_t)z * (s.vdim + 2)];
-            if (mz != -INFINITY) acc += p[(size_t)z * (s.vdim + 2) + 2 + d] * expf(mz - Mx);
+            const float f = __shfl_sync(0xFFFFFFFFu, fz, z);
+            if (d < s.vdim) acc = fmaf(p[(size_t)z * ps + 2 + d], f, acc);
         }
-        out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc / L * gate;
+        if (d < s.vdim) out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc / L * gate;
     }
 }
 

@@ -367,7 +367,7 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
     const size_t xs_bytes = (size_t)M * K * sizeof(float);
     if (few_rows(M, K)) {
         const int warps = kRowGemvThreads / 32;
-        const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * 2));
+        const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * 8));
         const Fuse f = fuse ? *fuse : Fuse{};
         if (m.d.mode == TI_SEQ_BF16)
             gemv_rows_kernel<__nv_bfloat16><<<grid, kRowGemvThreads, xs_bytes, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain,
@@ -639,9 +639,9 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.w0 = L.w0; a.u = L.u;
             a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d;
             const dim3 grid(E, L.d.heads);
-            if (d == 32) wkv_scan_reg_kernel<32><<<dim3(E, L.d.heads, 1), 32, 0, g_stream>>>(a, sm);
-            else if (d == 64) wkv_scan_reg_kernel<64><<<dim3(E, L.d.heads, 2), 32, 0, g_stream>>>(a, sm);
-            else if (d == 128) wkv_scan_reg_kernel<128><<<dim3(E, L.d.heads, 4), 32, 0, g_stream>>>(a, sm);
+            if (d == 32) wkv_scan_reg_kernel<32, 8><<<dim3(E, L.d.heads, 1), 32, 0, g_stream>>>(a, sm);
+            else if (d == 64) wkv_scan_reg_kernel<64, 8><<<dim3(E, L.d.heads, 2), 32, 0, g_stream>>>(a, sm);
+            else if (d == 128) wkv_scan_reg_kernel<128, 4><<<dim3(E, L.d.heads, 4), 32, 0, g_stream>>>(a, sm);
             else {
                 const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
                 a.s_in_smem = full <= g_smem_optin ? 1 : 0;

@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const float* A, int lda,
 // or scale, or the gated feed-forward's act(gate) * up over the row pair (n, n + glu_ff) of the fused [gate | up] matrix.
 // Bound by the weight bytes.
 constexpr int kRowGemvMaxRows = 8;
-constexpr int kRowGemvThreads = 512;
+constexpr int kRowGemvThreads = 256;
 __device__ __forceinline__ float ff_act(float z, int act);
 template <typename WT> __device__ __forceinline__ void load8(const WT* p, float (&w)[8]);
 template <> __device__ __forceinline__ void load8<float>(const float* p, float (&w)[8]) {
@@ -262,17 +262,25 @@ __device__ __forceinline__ void gemv_row_dot(const WT* w, const float* xs, int M
 #pragma unroll
     for (int r = 0; r < kRowGemvMaxRows; ++r) acc[r] = 0.f;
     if (vec) {
-#pragma unroll 2
-        for (int k = lane * 8; k < K; k += 256) {
-            float wv[8];
-            load8<WT>(w + k, wv);
+        constexpr int UNR = 4;   // 16-byte loads a lane has in flight before it starts multiplying
+        for (int k0 = lane * 8; k0 < K; k0 += 256 * UNR) {
+            float wv[UNR][8];
 #pragma unroll
-            for (int r = 0; r < kRowGemvMaxRows; ++r)
-                if (r < M) {
-                    const float4 a = *reinterpret_cast<const float4*>(xs + r * K + k), b = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
-                    acc[r] = fmaf(a.x, wv[0], fmaf(a.y, wv[1], fmaf(a.z, wv[2], fmaf(a.w, wv[3], acc[r]))));
-                    acc[r] = fmaf(b.x, wv[4], fmaf(b.y, wv[5], fmaf(b.z, wv[6], fmaf(b.w, wv[7], acc[r]))));
+            for (int q = 0; q < UNR; ++q)
+                if (k0 + 256 * q < K) load8<WT>(w + k0 + 256 * q, wv[q]);
+#pragma unroll
+            for (int q = 0; q < UNR; ++q) {
+                const int k = k0 + 256 * q;
+                if (k < K) {
+#pragma unroll
+                    for (int r = 0; r < kRowGemvMaxRows; ++r)
+                        if (r < M) {
+                            const float4 a = *reinterpret_cast<const float4*>(xs + r * K + k), b = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
+                            acc[r] = fmaf(a.x, wv[q][0], fmaf(a.y, wv[q][1], fmaf(a.z, wv[q][2], fmaf(a.w, wv[q][3], acc[r]))));
+                            acc[r] = fmaf(b.x, wv[q][4], fmaf(b.y, wv[q][5], fmaf(b.z, wv[q][6], fmaf(b.w, wv[q][7], acc[r]))));
+                        }
                 }
+            }
         }
     } else {
         for (int k = lane; k < K; k += 32) {
@@ -292,6 +300,18 @@ __global__ void __launch_bounds__(kRowGemvThreads) gemv_rows_kernel(const float*
     extern __shared__ __align__(16) float xs[];   // [M][K]
     __shared__ float rsc[kRowGemvMaxRows];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    {   // the weights do not depend on the rows: ask L2 for this warp's first column(s) before the rows are staged
+        const int n = blockIdx.x * nw + warp;
+        const size_t row_bytes = (size_t)K * sizeof(WT);
+        if (n < N) {
+            const char* w = reinterpret_cast<const char*>(W + (size_t)n * K);
+            for (size_t o = (size_t)lane * 128; o < row_bytes; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(w + o));
+            if (glu_ff > 0) {
+                const char* w2 = reinterpret_cast<const char*>(W + (size_t)(n + glu_ff) * K);
+                for (size_t o = (size_t)lane * 128; o < row_bytes; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(w2 + o));
+            }
+        }
+    }
     for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = A[(size_t)(i / K) * lda + (i % K)];
     __syncthreads();
     if (norm_gain) {
@@ -690,12 +710,14 @@ __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
     }
 }
 // head sizes 32 / 64 / 128: a WARP owns 32 value columns of a head (grid z = column group), each lane keeps its column of the
-// state in registers; the token's r / k / decay / u k vectors are double-buffered in shared memory behind a warp barrier and the
-// next token's operands are fetched while this one runs.  Four partial sums break the dependency chain of the output.
-template <int D>
+// state in registers.  Tokens are taken CH at a time: the chunk's r / k / decay / u k vectors are put into shared memory (decays
+// and u k computed there once), the NEXT chunk's operands are requested from memory, and then the chunk's tokens run back to
+// back -- the loop is bound by its arithmetic, not by one memory round trip per token.  Four partial sums break the dependency
+// chain of the output.
+template <int D, int CH>
 __global__ void __launch_bounds__(32) wkv_scan_reg_kernel(WkvArgs a, StepMeta m) {
     constexpr int PER = D / 32;   // elements of each token vector a lane fetches
-    __shared__ __align__(16) float buf[2][4][D];
+    __shared__ __align__(16) float buf[CH][4][D];
     const int e = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane;
     const int C = a.heads * D;
     float* Sg = a.state + ((size_t)m.ent_slot[e] * a.heads + hd) * (size_t)D * D;
@@ -703,61 +725,68 @@ __global__ void __launch_bounds__(32) wkv_scan_reg_kernel(WkvArgs a, StepMeta m)
     const bool fresh = (m.ent_pos0[e] == 0);
 #pragma unroll
     for (int i = 0; i < D; ++i) S[i] = fresh ? 0.f : Sg[i * D + j];
-    float w0[PER], u[PER], nr[PER], nk[PER], nz[PER];
+    float w0[PER], u[PER];
 #pragma unroll
     for (int p = 0; p < PER; ++p) {
         w0[p] = a.w0[hd * D + lane + 32 * p];
         u[p] = a.u[hd * D + lane + 32 * p];
     }
     const int t0 = m.ent_row0[e], t1 = m.ent_row0[e + 1];
-    size_t base = (size_t)t0 * C + (size_t)hd * D;
+    float nr[CH][PER], nk[CH][PER], nz[CH][PER], nv[CH];
+    auto fetch = [&](int tc) {
 #pragma unroll
-    for (int p = 0; p < PER; ++p) {
-        nr[p] = a.r[base + lane + 32 * p];
-        nk[p] = a.k[base + lane + 32 * p];
-        nz[p] = a.z[base + lane + 32 * p];
-    }
-    float nv = a.v[base + j];
-    for (int t = t0; t < t1; ++t) {
-        float(*b)[D] = buf[(t - t0) & 1];
-#pragma unroll
-        for (int p = 0; p < PER; ++p) {
-            b[0][lane + 32 * p] = nr[p];
-            b[1][lane + 32 * p] = nk[p];
-            b[2][lane + 32 * p] = expf(-expf(nz[p] + w0[p]));
-            b[3][lane + 32 * p] = u[p] * nk[p];
-        }
-        const float vj = nv;
-        const size_t obase = base;
-        if (t + 1 < t1) {
-            base += C;
+        for (int c = 0; c < CH; ++c) {
+            const bool ok = tc + c < t1;
+            const size_t base = (size_t)(ok ? tc + c : t1 - 1) * C + (size_t)hd * D;
 #pragma unroll
             for (int p = 0; p < PER; ++p) {
-                nr[p] = a.r[base + lane + 32 * p];
-                nk[p] = a.k[base + lane + 32 * p];
-                nz[p] = a.z[base + lane + 32 * p];
+                nr[c][p] = a.r[base + lane + 32 * p];
+                nk[c][p] = a.k[base + lane + 32 * p];
+                nz[c][p] = a.z[base + lane + 32 * p];
             }
-            nv = a.v[base + j];
+            nv[c] = a.v[base + j];
+        }
+    };
+    fetch(t0);
+    for (int tc = t0; tc < t1; tc += CH) {
+        float vj[CH];
+        __syncwarp();   // the previous chunk's reads of buf are done
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+#pragma unroll
+            for (int p = 0; p < PER; ++p) {
+                buf[c][0][lane + 32 * p] = nr[c][p];
+                buf[c][1][lane + 32 * p] = nk[c][p];
+                buf[c][2][lane + 32 * p] = expf(-expf(nz[c][p] + w0[p]));
+                buf[c][3][lane + 32 * p] = u[p] * nk[c][p];
+            }
+            vj[c] = nv[c];
         }
         __syncwarp();
-        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+        if (tc + CH < t1) fetch(tc + CH);
 #pragma unroll
-        for (int i = 0; i < D; i += 4) {
-            const float4 r4 = *reinterpret_cast<const float4*>(&b[0][i]);
-            const float4 k4 = *reinterpret_cast<const float4*>(&b[1][i]);
-            const float4 w4 = *reinterpret_cast<const float4*>(&b[2][i]);
-            const float4 u4 = *reinterpret_cast<const float4*>(&b[3][i]);
-            acc0 = fmaf(r4.x, fmaf(u4.x, vj, S[i]), acc0);
-            S[i] = fmaf(w4.x, S[i], k4.x * vj);
-            acc1 = fmaf(r4.y, fmaf(u4.y, vj, S[i + 1]), acc1);
-            S[i + 1] = fmaf(w4.y, S[i + 1], k4.y * vj);
-            acc2 = fmaf(r4.z, fmaf(u4.z, vj, S[i + 2]), acc2);
-            S[i + 2] = fmaf(w4.z, S[i + 2], k4.z * vj);
-            acc3 = fmaf(r4.w, fmaf(u4.w, vj, S[i + 3]), acc3);
-            S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * vj);
+        for (int c = 0; c < CH; ++c) {
+            if (tc + c < t1) {
+                float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+                const float v = vj[c];
+#pragma unroll
+                for (int i = 0; i < D; i += 4) {
+                    const float4 r4 = *reinterpret_cast<const float4*>(&buf[c][0][i]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&buf[c][1][i]);
+                    const float4 w4 = *reinterpret_cast<const float4*>(&buf[c][2][i]);
+                    const float4 u4 = *reinterpret_cast<const float4*>(&buf[c][3][i]);
+                    acc0 = fmaf(r4.x, fmaf(u4.x, v, S[i]), acc0);
+                    S[i] = fmaf(w4.x, S[i], k4.x * v);
+                    acc1 = fmaf(r4.y, fmaf(u4.y, v, S[i + 1]), acc1);
+                    S[i + 1] = fmaf(w4.y, S[i + 1], k4.y * v);
+                    acc2 = fmaf(r4.z, fmaf(u4.z, v, S[i + 2]), acc2);
+                    S[i + 2] = fmaf(w4.z, S[i + 2], k4.z * v);
+                    acc3 = fmaf(r4.w, fmaf(u4.w, v, S[i + 3]), acc3);
+                    S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * v);
+                }
+                a.out[(size_t)(tc + c) * C + (size_t)hd * D + j] = (acc0 + acc1) + (acc2 + acc3);
+            }
         }
-        a.out[obase + j] = (acc0 + acc1) + (acc2 + acc3);
-        // the buffer written two tokens from now is this one: every lane has read it by the warp barrier of the next token
     }
 #pragma unroll
     for (int i = 0; i < D; ++i) Sg[i * D + j] = S[i];
