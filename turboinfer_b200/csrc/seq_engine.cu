@@ -34,6 +34,7 @@ size_t g_smem_optin = 0;
 bool g_use_tiled_attn = true;   // TURBOINFER_B200_SEQ_TILED_ATTN=0: every row goes through the row-at-a-time attention kernel
 constexpr int kAttnTiledMinRows = 8;
 constexpr int kAttnMaxSplits = 16;    // key chunks of a decode row's attention   // portions at least this long are cut into attention tiles
+bool g_use_pdl = true;  // TURBOINFER_B200_SEQ_PDL=0: the few-row products wait for their predecessor before they start (A/B measurements)
 bool g_use_tc = true;   // TURBOINFER_B200_SEQ_TC=0: prompt-side products stay on the warp-level tensor path (A/B measurements)
 
 int fail(const char* fmt, ...) {
@@ -367,14 +368,27 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
     const size_t xs_bytes = (size_t)M * K * sizeof(float);
     if (few_rows(M, K)) {
         const int warps = kRowGemvThreads / 32;
-        const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * 8));
+        // enough resident blocks to keep the memory system busy, few enough that staging the rows in every block stays small
+        // beside the weight bytes: 2 blocks an SM (their registers allow no more) as far as their shared memory allows, columns looped inside
+        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, (200u << 10) / std::max<size_t>(xs_bytes, 1)));
+        const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * per_sm));
         const Fuse f = fuse ? *fuse : Fuse{};
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kRowGemvThreads);
+        cfg.dynamicSmemBytes = xs_bytes;
+        cfg.stream = g_stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_use_pdl ? 1 : 0;
         if (m.d.mode == TI_SEQ_BF16)
-            gemv_rows_kernel<__nv_bfloat16><<<grid, kRowGemvThreads, xs_bytes, g_stream>>>(A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain,
-                                                                                      f.eps, f.glu_ff, f.glu_act);
+            CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<__nv_bfloat16>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps,
+                                  f.glu_ff, f.glu_act));
         else
-            gemv_rows_kernel<float><<<grid, kRowGemvThreads, xs_bytes, g_stream>>>(A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
-                                                                              f.glu_act);
+            CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<float>, A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
+                                  f.glu_act));
         LAUNCHED();
         return 0;
     }
@@ -639,9 +653,9 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.w0 = L.w0; a.u = L.u;
             a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d;
             const dim3 grid(E, L.d.heads);
-            if (d == 32) wkv_scan_reg_kernel<32, 8><<<dim3(E, L.d.heads, 1), 32, 0, g_stream>>>(a, sm);
-            else if (d == 64) wkv_scan_reg_kernel<64, 8><<<dim3(E, L.d.heads, 2), 32, 0, g_stream>>>(a, sm);
-            else if (d == 128) wkv_scan_reg_kernel<128, 4><<<dim3(E, L.d.heads, 4), 32, 0, g_stream>>>(a, sm);
+            if (d == 32) wkv_scan_split_kernel<32, 8, 4><<<dim3(E, L.d.heads, 1), 128, 0, g_stream>>>(a, sm);
+            else if (d == 64) wkv_scan_split_kernel<64, 8, 4><<<dim3(E, L.d.heads, 2), 128, 0, g_stream>>>(a, sm);
+            else if (d == 128) wkv_scan_split_kernel<128, 4, 8><<<dim3(E, L.d.heads, 4), 256, 0, g_stream>>>(a, sm);
             else {
                 const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
                 a.s_in_smem = full <= g_smem_optin ? 1 : 0;
@@ -768,6 +782,7 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(gemv_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgSmemBytes));
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TC")) g_use_tc = atoi(e) != 0;
+    if (const char* e = getenv("TURBOINFER_B200_SEQ_PDL")) g_use_pdl = atoi(e) != 0;
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TILED_ATTN")) g_use_tiled_attn = atoi(e) != 0;
     CK(cudaFuncSetAttribute(window_attention_h3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_h3_smem_bytes<64>()));
     CK(cudaFuncSetAttribute(window_attention_h3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_h3_smem_bytes<128>()));

@@ -54,6 +54,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // x[t] = embed[tok[t]]; x0 (optional) keeps the embedding output for the looped block's input projection
 template <typename WT>
 __global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, float* x0) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     const int t = blockIdx.x;
     const WT* e = emb + (size_t)m.tok[t] * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
@@ -64,6 +65,7 @@ __global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, fl
 }
 // xc[t] = [x[t]; x0[t]]
 __global__ void concat_rows_kernel(const float* x, const float* x0, int D, float* xc) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     const int t = blockIdx.x;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         xc[(size_t)t * 2 * D + d] = x[(size_t)t * D + d];
@@ -74,6 +76,7 @@ __global__ void concat_rows_kernel(const float* x, const float* x0, int D, float
 // ---- RMS norm with one gain for all coordinates ----------------------------------------------------------------------
 // y[t] = x[row(t)] / sqrt(mean(x^2) + eps) * gain[0]; rows (optional) gathers (the rows whose logits are wanted)
 __global__ void scalar_rmsnorm_kernel(const float* x, const int* rows, int D, const float* gain, float eps, float* y) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     __shared__ float red[32];
     const int t = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[t] : t) * D;
@@ -86,6 +89,7 @@ __global__ void scalar_rmsnorm_kernel(const float* x, const int* rows, int D, co
 // x[t] += m[t] / sqrt(mean(m^2) + eps) * gain[0]   (the norm behind a sublayer, then the residual sum);
 // with gain2 != null it also writes the next sublayer's input y[t] = x[t] / rms(x[t]) * gain2[0]
 __global__ void postnorm_residual_kernel(float* x, const float* mo, int D, const float* gain, float eps, const float* gain2, float* y) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     __shared__ float red[32];
     const int t = blockIdx.x;
     const float* mr = mo + (size_t)t * D;
@@ -243,14 +247,20 @@ __global__ void __launch_bounds__(128) gemm_bf16_kernel(const float* A, int lda,
 constexpr int kRowGemvMaxRows = 8;
 constexpr int kRowGemvThreads = 256;
 __device__ __forceinline__ float ff_act(float z, int act);
-template <typename WT> __device__ __forceinline__ void load8(const WT* p, float (&w)[8]);
-template <> __device__ __forceinline__ void load8<float>(const float* p, float (&w)[8]) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+// eight consecutive weights as they lie in memory (kept packed while the loads are in flight) and as fp32
+template <typename WT> struct Raw8;
+template <> struct Raw8<float> { float4 a, b; };
+template <> struct Raw8<__nv_bfloat16> { uint4 v; };
+__device__ __forceinline__ void load_raw8(const float* p, Raw8<float>& r) {
+    r.a = *reinterpret_cast<const float4*>(p);
+    r.b = *reinterpret_cast<const float4*>(p + 4);
 }
-template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&w)[8]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+__device__ __forceinline__ void load_raw8(const __nv_bfloat16* p, Raw8<__nv_bfloat16>& r) { r.v = *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void unpack8(const Raw8<float>& r, float (&w)[8]) {
+    w[0] = r.a.x; w[1] = r.a.y; w[2] = r.a.z; w[3] = r.a.w; w[4] = r.b.x; w[5] = r.b.y; w[6] = r.b.z; w[7] = r.b.w;
+}
+__device__ __forceinline__ void unpack8(const Raw8<__nv_bfloat16>& r, float (&w)[8]) {
+    const uint32_t u[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         w[2 * i] = __uint_as_float(u[i] << 16);
@@ -262,22 +272,24 @@ __device__ __forceinline__ void gemv_row_dot(const WT* w, const float* xs, int M
 #pragma unroll
     for (int r = 0; r < kRowGemvMaxRows; ++r) acc[r] = 0.f;
     if (vec) {
-        constexpr int UNR = 4;   // 16-byte loads a lane has in flight before it starts multiplying
+        constexpr int UNR = 32 / (int)sizeof(Raw8<WT>) * 4;   // 16-byte loads a lane has in flight before it multiplies: 8 (bf16), 4 (fp32)
         for (int k0 = lane * 8; k0 < K; k0 += 256 * UNR) {
-            float wv[UNR][8];
+            Raw8<WT> raw[UNR];
 #pragma unroll
             for (int q = 0; q < UNR; ++q)
-                if (k0 + 256 * q < K) load8<WT>(w + k0 + 256 * q, wv[q]);
+                if (k0 + 256 * q < K) load_raw8(w + k0 + 256 * q, raw[q]);
 #pragma unroll
             for (int q = 0; q < UNR; ++q) {
                 const int k = k0 + 256 * q;
                 if (k < K) {
+                    float wv[8];
+                    unpack8(raw[q], wv);
 #pragma unroll
                     for (int r = 0; r < kRowGemvMaxRows; ++r)
                         if (r < M) {
                             const float4 a = *reinterpret_cast<const float4*>(xs + r * K + k), b = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
-                            acc[r] = fmaf(a.x, wv[q][0], fmaf(a.y, wv[q][1], fmaf(a.z, wv[q][2], fmaf(a.w, wv[q][3], acc[r]))));
-                            acc[r] = fmaf(b.x, wv[q][4], fmaf(b.y, wv[q][5], fmaf(b.z, wv[q][6], fmaf(b.w, wv[q][7], acc[r]))));
+                            acc[r] = fmaf(a.x, wv[0], fmaf(a.y, wv[1], fmaf(a.z, wv[2], fmaf(a.w, wv[3], acc[r]))));
+                            acc[r] = fmaf(b.x, wv[4], fmaf(b.y, wv[5], fmaf(b.z, wv[6], fmaf(b.w, wv[7], acc[r]))));
                         }
                 }
             }
@@ -294,13 +306,16 @@ __device__ __forceinline__ void gemv_row_dot(const WT* w, const float* xs, int M
     for (int r = 0; r < kRowGemvMaxRows; ++r)
         if (r < M) acc[r] = warp_sum(acc[r]);
 }
+// Launched with programmatic stream serialization: the block asks L2 for its first weight rows while the kernel before it is
+// still running, and only then waits for that kernel's results (the rows).
 template <typename WT>
-__global__ void __launch_bounds__(kRowGemvThreads) gemv_rows_kernel(const float* A, int lda, const WT* W, float* C, int ldc, int M, int N, int K, int epi,
+__global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const float* A, int lda, const WT* W, float* C, int ldc, int M, int N, int K, int epi,
                                                                   float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act) {
     extern __shared__ __align__(16) float xs[];   // [M][K]
-    __shared__ float rsc[kRowGemvMaxRows];
+    __shared__ float rss[kRowGemvMaxRows][kRowGemvThreads / 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    {   // the weights do not depend on the rows: ask L2 for this warp's first column(s) before the rows are staged
+    pdl_launch_dependents();
+    {   // the weights do not depend on the rows: ask L2 for this warp's first column(s) before the rows are there
         const int n = blockIdx.x * nw + warp;
         const size_t row_bytes = (size_t)K * sizeof(WT);
         if (n < N) {
@@ -312,19 +327,44 @@ __global__ void __launch_bounds__(kRowGemvThreads) gemv_rows_kernel(const float*
             }
         }
     }
-    for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = A[(size_t)(i / K) * lda + (i % K)];
+    pdl_wait_prior_grid();
+    // rows -> shared memory (rounded to the weight type when no norm comes first), sums of squares on the way
+    const bool vec4 = (K % 4 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    for (int r = 0; r < M; ++r) {
+        const float* ar = A + (size_t)r * lda;
+        float* xr = xs + (size_t)r * K;
+        float ss = 0.f;
+        if (vec4) {
+            for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
+                float4 v = *reinterpret_cast<const float4*>(ar + k);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                if (!norm_gain) { v.x = act_round<WT>(v.x); v.y = act_round<WT>(v.y); v.z = act_round<WT>(v.z); v.w = act_round<WT>(v.w); }
+                *reinterpret_cast<float4*>(xr + k) = v;
+            }
+        } else {
+            for (int k = threadIdx.x; k < K; k += blockDim.x) {
+                const float v = ar[k];
+                ss += v * v;
+                xr[k] = norm_gain ? v : act_round<WT>(v);
+            }
+        }
+        if (norm_gain) {
+            ss = warp_sum(ss);
+            if (lane == 0) rss[r][warp] = ss;
+        }
+    }
     __syncthreads();
     if (norm_gain) {
-        if (warp < M) {
+        const float g = norm_gain[0];
+        for (int r = 0; r < M; ++r) {
             float ss = 0.f;
-            for (int k = lane; k < K; k += 32) ss += xs[warp * K + k] * xs[warp * K + k];
-            ss = warp_sum(ss);
-            if (lane == 0) rsc[warp] = norm_gain[0] / sqrtf(ss / (float)K + eps);
+            for (int w = 0; w < nw; ++w) ss += rss[r][w];
+            const float sc = g / sqrtf(ss / (float)K + eps);
+            float* xr = xs + (size_t)r * K;
+            for (int k = threadIdx.x; k < K; k += blockDim.x) xr[k] = act_round<WT>(xr[k] * sc);
         }
         __syncthreads();
     }
-    for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = act_round<WT>(norm_gain ? xs[i] * rsc[i / K] : xs[i]);
-    __syncthreads();
     const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
     float acc[kRowGemvMaxRows], acc2[kRowGemvMaxRows];
     for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
@@ -350,6 +390,7 @@ struct AttnShape {
 // Rotation of q and k, unit RMS per head, and the cache append: one block per row.  q is rewritten in place; k and v go
 // to the row's page.  inv_freq[rot_dims / 2] holds the (scaled) frequencies; the angle is position * frequency in fp32.
 __global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const float* inv_freq, float* k_pool, float* v_pool) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     const int t = blockIdx.x;
     const int pos = m.row_pos[t];
     const int slot = m.ent_slot[m.row_ent[t]];
@@ -397,6 +438,7 @@ constexpr int kAttnWarps = 4;
 constexpr int kAttnMaxPerLane = 8;   // head sizes up to 256
 __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const float* qkvg, StepMeta m, AttnShape s, const int* rows,
                                                                             const float* k_pool, const float* v_pool, float* out) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     extern __shared__ float sm[];   // [kAttnWarps][dv] partial outputs, then [kAttnWarps] max, [kAttnWarps] sum
     const int t = rows ? rows[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -634,6 +676,7 @@ __global__ void glu_kernel(const float* gu, int ff, int act, float* y, size_t n)
 // saved row for an entry's first row, zeros at position 0.
 __global__ void wkv_mix_kernel(const float* h, StepMeta m, int D, const float* mu /*[5][D]*/, const float* prev_state /*[slots][D]*/,
                                float* mixes /*[5][T][D]*/) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     const int t = blockIdx.x;
     const int e = m.row_ent[t];
     const bool first = (t == m.ent_row0[e]);
@@ -647,6 +690,7 @@ __global__ void wkv_mix_kernel(const float* h, StepMeta m, int D, const float* m
 }
 // the slot keeps the mixer input of the entry's last row for the next step
 __global__ void wkv_save_prev_kernel(const float* h, StepMeta m, int D, float* prev_state) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     const int e = blockIdx.x;
     const int t = m.ent_row0[e + 1] - 1;
     for (int d = threadIdx.x; d < D; d += blockDim.x) prev_state[(size_t)m.ent_slot[e] * D + d] = h[(size_t)t * D + d];
@@ -665,6 +709,7 @@ struct WkvArgs {
 };
 // any head size: S in shared memory while the entry's rows run (in global memory directly when it does not fit)
 __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     extern __shared__ float sm[];
     const int e = blockIdx.x, hd = blockIdx.y, d = a.dim, j = threadIdx.x;
     const int C = a.heads * d;
@@ -709,72 +754,96 @@ __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
         for (int i = 0; i < d; ++i) Sg[i * d + j] = S[i * d + j];
     }
 }
-// head sizes 32 / 64 / 128: a WARP owns 32 value columns of a head (grid z = column group), each lane keeps its column of the
-// state in registers.  Tokens are taken CH at a time: the chunk's r / k / decay / u k vectors are put into shared memory (decays
-// and u k computed there once), the NEXT chunk's operands are requested from memory, and then the chunk's tokens run back to
-// back -- the loop is bound by its arithmetic, not by one memory round trip per token.  Four partial sums break the dependency
-// chain of the output.
-template <int D, int CH>
-__global__ void __launch_bounds__(32) wkv_scan_reg_kernel(WkvArgs a, StepMeta m) {
-    constexpr int PER = D / 32;   // elements of each token vector a lane fetches
+// head sizes 32 / 64 / 128: a BLOCK owns 32 value columns of a head (grid z = column group); its NW warps split the key
+// channels, so a lane keeps D / NW entries of its state column in registers and a token costs D / NW multiply-adds a lane
+// instead of D.  Tokens are taken CH at a time: the block puts the chunk's r / k / decay / u k vectors and its v columns into
+// shared memory (decays and u k computed there once), requests the NEXT chunk's operands from memory, and then every warp runs
+// the chunk's tokens back to back over its key channels and leaves a partial output per token; the partials of the NW warps
+// are summed (in warp order, so the result does not depend on timing) while the next chunk is staged.  Two block barriers a chunk.
+template <int D, int CH, int NW>
+__global__ void __launch_bounds__(32 * NW) wkv_scan_split_kernel(WkvArgs a, StepMeta m) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    constexpr int RP = D / NW;          // key channels a warp owns
+    constexpr int NT = 32 * NW;
+    constexpr int PER = CH * D / NT;    // operands of each kind a thread stages per chunk
+    constexpr int VPER = (CH * 32 + NT - 1) / NT;
+    static_assert(D % NW == 0 && RP % 4 == 0 && (CH * D) % NT == 0, "chunk staging must divide evenly");
     __shared__ __align__(16) float buf[CH][4][D];
-    const int e = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane;
+    __shared__ float vbuf[CH][32];
+    __shared__ float part[NW][CH][32];
+    const int e = blockIdx.x, hd = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int col0 = blockIdx.z * 32, j = col0 + lane;
     const int C = a.heads * D;
     float* Sg = a.state + ((size_t)m.ent_slot[e] * a.heads + hd) * (size_t)D * D;
-    float S[D];
+    float S[RP];
     const bool fresh = (m.ent_pos0[e] == 0);
 #pragma unroll
-    for (int i = 0; i < D; ++i) S[i] = fresh ? 0.f : Sg[i * D + j];
+    for (int i = 0; i < RP; ++i) S[i] = fresh ? 0.f : Sg[(size_t)(warp * RP + i) * D + j];
     float w0[PER], u[PER];
 #pragma unroll
     for (int p = 0; p < PER; ++p) {
-        w0[p] = a.w0[hd * D + lane + 32 * p];
-        u[p] = a.u[hd * D + lane + 32 * p];
+        const int i = (tid + NT * p) % D;
+        w0[p] = a.w0[hd * D + i];
+        u[p] = a.u[hd * D + i];
     }
     const int t0 = m.ent_row0[e], t1 = m.ent_row0[e + 1];
-    float nr[CH][PER], nk[CH][PER], nz[CH][PER], nv[CH];
+    float nr[PER], nk[PER], nz[PER], nv[VPER];
     auto fetch = [&](int tc) {
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const bool ok = tc + c < t1;
-            const size_t base = (size_t)(ok ? tc + c : t1 - 1) * C + (size_t)hd * D;
+        for (int p = 0; p < PER; ++p) {
+            const int q = tid + NT * p, c = q / D, i = q % D;
+            const size_t base = (size_t)min(tc + c, t1 - 1) * C + (size_t)hd * D + i;
+            nr[p] = a.r[base];
+            nk[p] = a.k[base];
+            nz[p] = a.z[base];
+        }
 #pragma unroll
-            for (int p = 0; p < PER; ++p) {
-                nr[c][p] = a.r[base + lane + 32 * p];
-                nk[c][p] = a.k[base + lane + 32 * p];
-                nz[c][p] = a.z[base + lane + 32 * p];
+        for (int p = 0; p < VPER; ++p) {
+            const int q = tid + NT * p, c = q >> 5, l = q & 31;
+            nv[p] = c < CH ? a.v[(size_t)min(tc + c, t1 - 1) * C + (size_t)hd * D + col0 + l] : 0.f;
+        }
+    };
+    auto emit = [&](int tc) {   // out[t][j] = sum over the warps' partials, chunk starting at row tc
+        for (int q = tid; q < CH * 32; q += NT) {
+            const int c = q >> 5, l = q & 31;
+            if (tc + c < t1) {
+                float s = part[0][c][l];
+#pragma unroll
+                for (int w = 1; w < NW; ++w) s += part[w][c][l];
+                a.out[(size_t)(tc + c) * C + (size_t)hd * D + col0 + l] = s;
             }
-            nv[c] = a.v[base + j];
         }
     };
     fetch(t0);
     for (int tc = t0; tc < t1; tc += CH) {
-        float vj[CH];
-        __syncwarp();   // the previous chunk's reads of buf are done
+        if (tc > t0) emit(tc - CH);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-#pragma unroll
-            for (int p = 0; p < PER; ++p) {
-                buf[c][0][lane + 32 * p] = nr[c][p];
-                buf[c][1][lane + 32 * p] = nk[c][p];
-                buf[c][2][lane + 32 * p] = expf(-expf(nz[c][p] + w0[p]));
-                buf[c][3][lane + 32 * p] = u[p] * nk[c][p];
-            }
-            vj[c] = nv[c];
+        for (int p = 0; p < PER; ++p) {
+            const int q = tid + NT * p, c = q / D, i = q % D;
+            buf[c][0][i] = nr[p];
+            buf[c][1][i] = nk[p];
+            buf[c][2][i] = expf(-expf(nz[p] + w0[p]));
+            buf[c][3][i] = u[p] * nk[p];
         }
-        __syncwarp();
+#pragma unroll
+        for (int p = 0; p < VPER; ++p) {
+            const int q = tid + NT * p;
+            if (q < CH * 32) vbuf[q >> 5][q & 31] = nv[p];
+        }
+        __syncthreads();
         if (tc + CH < t1) fetch(tc + CH);
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
             if (tc + c < t1) {
                 float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-                const float v = vj[c];
+                const float v = vbuf[c][lane];
 #pragma unroll
-                for (int i = 0; i < D; i += 4) {
-                    const float4 r4 = *reinterpret_cast<const float4*>(&buf[c][0][i]);
-                    const float4 k4 = *reinterpret_cast<const float4*>(&buf[c][1][i]);
-                    const float4 w4 = *reinterpret_cast<const float4*>(&buf[c][2][i]);
-                    const float4 u4 = *reinterpret_cast<const float4*>(&buf[c][3][i]);
+                for (int i = 0; i < RP; i += 4) {
+                    const int ch = warp * RP + i;
+                    const float4 r4 = *reinterpret_cast<const float4*>(&buf[c][0][ch]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&buf[c][1][ch]);
+                    const float4 w4 = *reinterpret_cast<const float4*>(&buf[c][2][ch]);
+                    const float4 u4 = *reinterpret_cast<const float4*>(&buf[c][3][ch]);
                     acc0 = fmaf(r4.x, fmaf(u4.x, v, S[i]), acc0);
                     S[i] = fmaf(w4.x, S[i], k4.x * v);
                     acc1 = fmaf(r4.y, fmaf(u4.y, v, S[i + 1]), acc1);
@@ -784,15 +853,18 @@ __global__ void __launch_bounds__(32) wkv_scan_reg_kernel(WkvArgs a, StepMeta m)
                     acc3 = fmaf(r4.w, fmaf(u4.w, v, S[i + 3]), acc3);
                     S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * v);
                 }
-                a.out[(size_t)(tc + c) * C + (size_t)hd * D + j] = (acc0 + acc1) + (acc2 + acc3);
+                part[warp][c][lane] = (acc0 + acc1) + (acc2 + acc3);
             }
         }
+        __syncthreads();
     }
+    emit(t0 + (t1 - t0 - 1) / CH * CH);
 #pragma unroll
-    for (int i = 0; i < D; ++i) Sg[i * D + j] = S[i];
+    for (int i = 0; i < RP; ++i) Sg[(size_t)(warp * RP + i) * D + j] = S[i];
 }
 // o[t, head] / rms(o[t, head]) * normw * gate, in place: one warp per (row, head)
 __global__ void wkv_finish_kernel(float* o, const float* gate, const float* normw, int T, int heads, int d, float eps) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= T * heads) return;
     const int hd = warp % heads;
@@ -806,6 +878,7 @@ __global__ void wkv_finish_kernel(float* o, const float* gate, const float* norm
 
 // ---- helpers -----------------------------------------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const float* x, const int* rows, int D, float* y) {
+    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
     const int t = blockIdx.x;
     for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = x[(size_t)rows[t] * D + d];
 }
