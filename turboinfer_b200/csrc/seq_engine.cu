@@ -122,8 +122,15 @@ __global__ void argmax_rows_kernel(const float* logits, int V, int ld, int* tok,
     const float* r = logits + (size_t)blockIdx.x * ld;
     float best = -INFINITY;
     int idx = 0x7FFFFFFF;
-    for (int i = threadIdx.x; i < V; i += blockDim.x)
-        if (r[i] > best) { best = r[i]; idx = i; }
+    const int bd = blockDim.x;
+    for (int i = threadIdx.x; i < V; i += 4 * bd) {   // four independent loads a pass, compared in ascending index order
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = i + q * bd < V ? r[i + q * bd] : -INFINITY;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (v[q] > best) { best = v[q]; idx = i + q * bd; }
+    }
     for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
         const int oi = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
@@ -136,7 +143,12 @@ __global__ void argmax_rows_kernel(const float* logits, int V, int ld, int* tok,
     for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
         if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
     float s = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) s += expf(r[i] - best);
+    for (int i = threadIdx.x; i < V; i += 4 * bd) {
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = i + q * bd < V ? r[i + q * bd] : -INFINITY;
+        s += (expf(v[0] - best) + expf(v[1] - best)) + (expf(v[2] - best) + expf(v[3] - best));
+    }
     s = block_sum(s, red);
     if (threadIdx.x == 0) {
         tok[blockIdx.x] = idx == 0x7FFFFFFF ? 0 : idx;
@@ -444,6 +456,39 @@ int ensure_scratch(Model& m, int rows, int want) {
 }
 
 // ---- the step ----------------------------------------------------------------------------------------------------------------
+// few rows: the wkv mixer's r / k / v / g / decay-input products with their mixes built in the prologue (one launch)
+int wkv_front(Model& m, LayerW& L, Run& R, const StepMeta& sm, int T, float* pr, float* pk, float* pv, float* pg, float* lora) {
+    const int D = m.d.width, C = L.d.heads * L.d.dim, rank = L.d.decay_rank;
+    WkvFrontArgs a{};
+    a.h = m.h.p; a.mu = L.mu.p; a.prev = R.prev.p; a.D = D;
+    const void* W[5] = {L.r, L.k, L.v, L.g, L.w1};
+    float* out[5] = {pr, pk, pv, pg, lora};
+    const int N[5] = {C, C, C, C, rank}, epi[5] = {EPI_NONE, EPI_NONE, EPI_NONE, EPI_SILU, EPI_TANH};
+    const int warps = kRowGemvThreads / 32, budget = 2 * g_num_sms;
+    const long total = 4L * C + rank;
+    a.blk0[0] = 0;
+    for (int s = 0; s < 5; ++s) {
+        a.W[s] = W[s]; a.out[s] = out[s]; a.N[s] = N[s]; a.epi[s] = epi[s];
+        const int want = (N[s] + warps - 1) / warps;
+        const int share = (int)std::max<long>(1, (long)budget * N[s] / total);
+        a.blk0[s + 1] = a.blk0[s] + std::max(1, std::min(want, share));
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(a.blk0[5]);
+    cfg.blockDim = dim3(kRowGemvThreads);
+    cfg.dynamicSmemBytes = (size_t)T * D * sizeof(float);
+    cfg.stream = g_stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    if (m.d.mode == TI_SEQ_BF16) CK(cudaLaunchKernelEx(&cfg, wkv_front_rows_kernel<__nv_bfloat16>, a, sm));
+    else CK(cudaLaunchKernelEx(&cfg, wkv_front_rows_kernel<float>, a, sm));
+    LAUNCHED();
+    return 0;
+}
+
 struct SampleSpec {
     bool on = false;
     float temperature = 0.f, top_p = 1.f;
@@ -636,17 +681,23 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             TRY(gemm(m, m.att.p, s.heads * s.vdim, L.o, m.mo.p, D, T, D, s.heads * s.vdim));
         } else {
             const int C = L.d.heads * L.d.dim, d = L.d.dim, rank = L.d.decay_rank;
-            wkv_mix_kernel<<<T, nt, 0, g_stream>>>(m.h.p, sm, D, L.mu.p, R.prev.p, m.mixes.p);
-            LAUNCHED();
-            wkv_save_prev_kernel<<<E, nt, 0, g_stream>>>(m.h.p, sm, D, R.prev.p);
-            LAUNCHED();
             const size_t TD = (size_t)T * D, TC = (size_t)T * C;
             float *pr = m.proj.p, *pk = pr + TC, *pv = pk + TC, *pg = pv + TC, *pz = pg + TC;
-            TRY(gemm(m, m.mixes.p + 0 * TD, D, L.r, pr, C, T, C, D));
-            TRY(gemm(m, m.mixes.p + 1 * TD, D, L.k, pk, C, T, C, D));
-            TRY(gemm(m, m.mixes.p + 2 * TD, D, L.v, pv, C, T, C, D));
-            TRY(gemm(m, m.mixes.p + 3 * TD, D, L.g, pg, C, T, C, D, EPI_SILU));
-            TRY(gemm(m, m.mixes.p + 4 * TD, D, L.w1, m.lora.p, rank, T, rank, D, EPI_TANH));
+            if (fuse_rows) {   // the five input products and their token-shift mixes in one launch
+                TRY(wkv_front(m, L, R, sm, T, pr, pk, pv, pg, m.lora.p));
+                wkv_save_prev_kernel<<<E, nt, 0, g_stream>>>(m.h.p, sm, D, R.prev.p);
+                LAUNCHED();
+            } else {
+                wkv_mix_kernel<<<T, nt, 0, g_stream>>>(m.h.p, sm, D, L.mu.p, R.prev.p, m.mixes.p);
+                LAUNCHED();
+                wkv_save_prev_kernel<<<E, nt, 0, g_stream>>>(m.h.p, sm, D, R.prev.p);
+                LAUNCHED();
+                TRY(gemm(m, m.mixes.p + 0 * TD, D, L.r, pr, C, T, C, D));
+                TRY(gemm(m, m.mixes.p + 1 * TD, D, L.k, pk, C, T, C, D));
+                TRY(gemm(m, m.mixes.p + 2 * TD, D, L.v, pv, C, T, C, D));
+                TRY(gemm(m, m.mixes.p + 3 * TD, D, L.g, pg, C, T, C, D, EPI_SILU));
+                TRY(gemm(m, m.mixes.p + 4 * TD, D, L.w1, m.lora.p, rank, T, rank, D, EPI_TANH));
+            }
             TRY(gemm(m, m.lora.p, rank, L.w2, pz, C, T, C, rank));
             WkvArgs a{};
             a.r = pr; a.k = pk; a.v = pv; a.z = pz;
@@ -705,7 +756,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     if (smp.on) {
         const bool greedy = !(smp.temperature > 0.f) || smp.top_k == 1;
         if (greedy) {
-            argmax_rows_kernel<<<E, 256, 0, g_stream>>>(m.logits.p, V, V, m.picks.p, m.logprobs.p);
+            argmax_rows_kernel<<<E, 1024, 0, g_stream>>>(m.logits.p, V, V, m.picks.p, m.logprobs.p);
             LAUNCHED();
         } else {
             const size_t row_smem = sample_row_smem_bytes(V);
@@ -779,6 +830,8 @@ int ti_seq_init(int device) {
     g_smem_optin = std::min<size_t>(p.sharedMemPerBlockOptin, 200 * 1024);
     if (!g_stream) CK(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(wkv_front_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(wkv_front_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgSmemBytes));
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TC")) g_use_tc = atoi(e) != 0;

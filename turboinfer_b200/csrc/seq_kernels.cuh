@@ -378,6 +378,62 @@ __global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const flo
     }
 }
 
+// The five input products of the wkv mixer for few rows in ONE launch: r, k, v, g and the decay's first matrix each read their
+// own token-shift mix x_s = h + (prev - h) * mu_s, so a block works on one of the five products, builds that product's mix of
+// the rows in shared memory (no mixes in global memory) and streams its share of that product's weight rows.
+struct WkvFrontArgs {
+    const float* h;      // [T][D] mixer input rows
+    const float* mu;     // [5][D]: r, k, v, g, w
+    const float* prev;   // [slots][D]: the mixer input of each sequence's last row of the step before
+    const void* W[5];
+    float* out[5];       // [T][N[s]]
+    int N[5], epi[5];
+    int blk0[6];         // blocks blk0[s] .. blk0[s + 1] - 1 work on product s
+    int D;
+};
+template <typename WT>
+__global__ void __launch_bounds__(kRowGemvThreads, 2) wkv_front_rows_kernel(WkvFrontArgs a, StepMeta m) {
+    extern __shared__ __align__(16) float xs[];   // [T][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    pdl_launch_dependents();
+    int s = 0;
+    while (s < 4 && (int)blockIdx.x >= a.blk0[s + 1]) ++s;
+    const int b = blockIdx.x - a.blk0[s], nb = a.blk0[s + 1] - a.blk0[s];
+    const WT* W = reinterpret_cast<const WT*>(a.W[s]);
+    const int N = a.N[s], K = a.D, M = m.T;
+    {
+        const int n = b * nw + warp;
+        if (n < N) {
+            const char* w = reinterpret_cast<const char*>(W + (size_t)n * K);
+            for (size_t o = (size_t)lane * 128; o < (size_t)K * sizeof(WT); o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(w + o));
+        }
+    }
+    pdl_wait_prior_grid();
+    const float* mu = a.mu + (size_t)s * K;
+    for (int r = 0; r < M; ++r) {
+        const int e = m.row_ent[r];
+        const bool first = (r == m.ent_row0[e]);
+        const float* pr = first ? (m.ent_pos0[e] > 0 ? a.prev + (size_t)m.ent_slot[e] * K : nullptr) : a.h + (size_t)(r - 1) * K;
+        const float* hr = a.h + (size_t)r * K;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+            const float hv = hr[k];
+            const float df = (pr ? pr[k] : 0.f) - hv;
+            xs[(size_t)r * K + k] = act_round<WT>(fmaf(df, mu[k], hv));
+        }
+    }
+    __syncthreads();
+    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
+    float acc[kRowGemvMaxRows];
+    for (int n = b * nw + warp; n < N; n += nb * nw) {
+        gemv_row_dot<WT>(W + (size_t)n * K, xs, M, K, vec, lane, acc);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < kRowGemvMaxRows; ++r)
+                if (r < M) a.out[s][(size_t)r * N + n] = epi_apply(acc[r], a.epi[s], 1.f);
+        }
+    }
+}
+
 // ---- attention -------------------------------------------------------------------------------------------------------
 struct AttnShape {
     int heads, kv_heads, dim, vdim;   // H, G, d, dv
