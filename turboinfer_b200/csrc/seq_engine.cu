@@ -663,10 +663,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 LAUNCHED();
             }
             if (n_rest > 0) {
-                // single rows: key chunks in parallel when the visible span is long and the rows alone would not fill the GPU
+                // single rows: key chunks in parallel (a row-at-a-time walk is one memory round trip a key) unless the rows alone fill the GPU
                 const int span = s.window > 0 ? std::min(s.window, max_pos + 1) : max_pos + 1;
                 int splits = 1;
-                if (span >= 256) splits = std::max(1, std::min({span / 64, kAttnMaxSplits, (2 * g_num_sms) / std::max(1, n_rest * s.heads)}));
+                if (span >= 32) splits = std::max(1, std::min({(span + 15) / 16, kAttnMaxSplits, (2 * g_num_sms) / std::max(1, n_rest * s.heads)}));
                 if (splits > 1 && m.attn_part.p) {
                     window_attention_split_kernel<<<dim3(n_rest, s.heads, splits), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, rest, splits, R.k_pool.p,
                                                                                                                         R.v_pool.p, m.attn_part.p);
@@ -705,8 +705,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d;
             const dim3 grid(E, L.d.heads);
             if (d == 32) wkv_scan_split_kernel<32, 8, 4><<<dim3(E, L.d.heads, 1), 128, 0, g_stream>>>(a, sm);
-            else if (d == 64) wkv_scan_split_kernel<64, 8, 4><<<dim3(E, L.d.heads, 2), 128, 0, g_stream>>>(a, sm);
-            else if (d == 128) wkv_scan_split_kernel<128, 4, 8><<<dim3(E, L.d.heads, 4), 256, 0, g_stream>>>(a, sm);
+            else if (d == 64) wkv_scan_split_kernel<64, 8, 8><<<dim3(E, L.d.heads, 2), 256, 0, g_stream>>>(a, sm);
+            else if (d == 128) wkv_scan_split_kernel<128, 4, 16><<<dim3(E, L.d.heads, 4), 512, 0, g_stream>>>(a, sm);
             else {
                 const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
                 a.s_in_smem = full <= g_smem_optin ? 1 : 0;
