@@ -263,6 +263,50 @@ def test_greedy_generation_continuous_batching():
     assert seq == want[1]
 
 
+def test_command_line_generate_and_trace_replay(tmp_path):
+    """A checkpoint folder on disk through the registry: bin/generate (continuous batching) and bin/trace_run (step by step)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from binusun_cases import public_config
+    from turboinfer_b200.safetensors_io import write_safetensors
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    cfg = make_config([attn_layer(window=9, ff=40), wkv_layer()], loop=(1, 2, 2), vocab=53)
+    W = random_weights(cfg, seed=23)
+    folder = os.path.join(tmp_path, "model")
+    os.makedirs(folder)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(public_config(cfg), f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), W)
+    prompts = [tokens(7, 53, 3), tokens(30, 53, 4)]
+    want = [plain_greedy(cfg, W, p, 6) for p in prompts]
+    cmd = [sys.executable, os.path.join(root, "bin", "generate"), "--model", folder, "--dtype", "float32", "--max-new", "6"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(str(t) for t in p)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr
+    got = [json.loads(line)["tokens"] for line in res.stdout.splitlines() if line.startswith("{")]
+    assert got == want
+    # the same prompt replayed in three steps, logits asked for at two places of the last one
+    out = os.path.join(tmp_path, "out")
+    os.makedirs(out)
+    p = prompts[1]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": p[:11], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": p[11:13], "want": []}, {"id": "b", "tokens": prompts[0], "want": [6]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": p[13:], "want": [0, len(p) - 14]}], "end": ["a"]}]
+    res = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", out,
+                          "--max-tokens", "128"], input="".join(json.dumps(x) + "\n" for x in steps), capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr
+    assert [ln for ln in res.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not os.path.exists(os.path.join(out, "0.f32"))
+    ref_a, ref_b = plain.forward(cfg, W, p), plain.forward(cfg, W, prompts[0])
+    l1 = np.fromfile(os.path.join(out, "1.f32"), "<f4").reshape(1, 53)
+    l2 = np.fromfile(os.path.join(out, "2.f32"), "<f4").reshape(2, 53)
+    assert rel_err(l1, ref_b[[6]]) < TOL["float32"]
+    assert rel_err(l2, ref_a[[13, len(p) - 1]]) < TOL["float32"]
+
+
 def test_sampling_is_reproducible_and_respects_top_k():
     cfg = make_config([attn_layer()], vocab=61)
     W = random_weights(cfg, seed=17)
