@@ -178,7 +178,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) window_attention_h3_kernel(cons
 // `part`; attention_merge_kernel combines the splits and applies the gate.  chunk = ceil(visible keys / splits).
 __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel(const float* qkvg, StepMeta m, AttnShape s, const int* rows, int splits,
                                                                                   const float* k_pool, const float* v_pool, float* part) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     extern __shared__ float sm[];
     const int bx = blockIdx.x, t = rows ? rows[bx] : bx, h = blockIdx.y, z = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -269,7 +270,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
 }
 // one warp per (row, head): lane z holds split z's (max, sum); the output coordinates are spread over the lanes
 __global__ void attention_merge_kernel(const float* part, const float* qkvg, StepMeta m, AttnShape s, const int* rows, int n_rows, int splits, float* out) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (wid >= n_rows * s.heads) return;
     const int bx = wid / s.heads, h = wid % s.heads, t = rows ? rows[bx] : bx;

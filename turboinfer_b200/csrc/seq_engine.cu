@@ -116,6 +116,8 @@ __global__ void synth_fill_f32_kernel(float* out, size_t n, uint64_t seed, float
 }
 // first maximum of every row (temperature 0); its log-probability under softmax(logits) when asked for
 __global__ void argmax_rows_kernel(const float* logits, int V, int ld, int* tok, float* logprob) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
     __shared__ float bv[32];
     __shared__ int bi[32];
     __shared__ float red[32];
@@ -367,6 +369,25 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t r
 // ---- matrix product dispatch ----------------------------------------------------------------------------------------------
 // Fusion a caller may ask for; it happens inside the product when the step is a decode step (few rows) and the caller does the
 // separate kernel otherwise (gemm() says which through the return of fused()).
+// Launch of a kernel of the step with programmatic stream serialization: it may be scheduled while the kernel before it is still
+// running and parks in griddepcontrol.wait (the first statement of every kernel launched through here) until that one has
+// completed, so the launch latency of the many small kernels of a decode step overlaps the kernel in front.
+template <typename... KArgs, typename... Args>
+int launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = g_stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    CK(cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...));
+    return 0;   // (the caller counts the launch)
+}
+
 struct Fuse {
     const float* norm_gain = nullptr;   // scalar-gain RMS norm of the input rows in front of the product
     float eps = 0.f;
@@ -609,15 +630,15 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     CK(cudaEventRecord(m.ev0, g_stream));
     const bool bf = m.d.mode == TI_SEQ_BF16;
     const int nt = 256;
-    if (bf) embed_rows_kernel<__nv_bfloat16><<<T, nt, 0, g_stream>>>((const __nv_bfloat16*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr);
-    else embed_rows_kernel<float><<<T, nt, 0, g_stream>>>((const float*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr);
+    if (bf) TRY(launch_dep(embed_rows_kernel<__nv_bfloat16>, dim3(T), dim3(nt), 0, (const __nv_bfloat16*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr));
+    else TRY(launch_dep(embed_rows_kernel<float>, dim3(T), dim3(nt), 0, (const float*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr));
     LAUNCHED();
     const float eps = m.d.norm_eps;
     for (size_t ri = 0; ri < m.runs.size(); ++ri) {
         Run& R = m.runs[ri];
         LayerW& L = m.layers[R.layer];
         if (R.enters_pass) {
-            concat_rows_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.x0.p, D, m.xc.p);
+            TRY(launch_dep(concat_rows_kernel, dim3(T), dim3(nt), 0, m.x.p, m.x0.p, D, m.xc.p));
             LAUNCHED();
             TRY(gemm(m, m.xc.p, 2 * D, m.loop_in, m.x.p, D, T, D, 2 * D));
         }
@@ -625,7 +646,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         const bool fuse_rows = few_rows(T, D);
         const bool attn = L.d.mixer == TI_SEQ_MIXER_ATTENTION;
         if (!(fuse_rows && attn)) {
-            scalar_rmsnorm_kernel<<<T, nt, 0, g_stream>>>(m.x.p, nullptr, D, L.norm1, eps, m.h.p);
+            TRY(launch_dep(scalar_rmsnorm_kernel, dim3(T), dim3(nt), 0, m.x.p, nullptr, D, L.norm1, eps, m.h.p));
             LAUNCHED();
         }
         if (attn) {
@@ -640,7 +661,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             } else {
                 TRY(gemm(m, m.h.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
             }
-            attn_prepare_kernel<<<T, 128, 0, g_stream>>>(m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p);
+            TRY(launch_dep(attn_prepare_kernel, dim3(T), dim3(128), 0, m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p));
             LAUNCHED();
             const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
             const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim);
@@ -668,13 +689,13 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 int splits = 1;
                 if (span >= 32) splits = std::max(1, std::min({(span + 15) / 16, kAttnMaxSplits, (2 * g_num_sms) / std::max(1, n_rest * s.heads)}));
                 if (splits > 1 && m.attn_part.p) {
-                    window_attention_split_kernel<<<dim3(n_rest, s.heads, splits), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, rest, splits, R.k_pool.p,
-                                                                                                                        R.v_pool.p, m.attn_part.p);
+                    TRY(launch_dep(window_attention_split_kernel, dim3(n_rest, s.heads, splits), dim3(kAttnWarps * 32), smem, m.proj.p, sm, s, rest, splits, R.k_pool.p,
+                                                                                                                        R.v_pool.p, m.attn_part.p));
                     LAUNCHED();
-                    attention_merge_kernel<<<(n_rest * s.heads + 7) / 8, 256, 0, g_stream>>>(m.attn_part.p, m.proj.p, sm, s, rest, n_rest, splits, m.att.p);
+                    TRY(launch_dep(attention_merge_kernel, dim3((n_rest * s.heads + 7) / 8), dim3(256), 0, m.attn_part.p, m.proj.p, sm, s, rest, n_rest, splits, m.att.p));
                     LAUNCHED();
                 } else {
-                    window_attention_kernel<<<dim3(n_rest, s.heads), kAttnWarps * 32, smem, g_stream>>>(m.proj.p, sm, s, rest, R.k_pool.p, R.v_pool.p, m.att.p);
+                    TRY(launch_dep(window_attention_kernel, dim3(n_rest, s.heads), dim3(kAttnWarps * 32), smem, m.proj.p, sm, s, rest, R.k_pool.p, R.v_pool.p, m.att.p));
                     LAUNCHED();
                 }
             }
@@ -685,12 +706,12 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             float *pr = m.proj.p, *pk = pr + TC, *pv = pk + TC, *pg = pv + TC, *pz = pg + TC;
             if (fuse_rows) {   // the five input products and their token-shift mixes in one launch
                 TRY(wkv_front(m, L, R, sm, T, pr, pk, pv, pg, m.lora.p));
-                wkv_save_prev_kernel<<<E, nt, 0, g_stream>>>(m.h.p, sm, D, R.prev.p);
+                TRY(launch_dep(wkv_save_prev_kernel, dim3(E), dim3(nt), 0, m.h.p, sm, D, R.prev.p));
                 LAUNCHED();
             } else {
-                wkv_mix_kernel<<<T, nt, 0, g_stream>>>(m.h.p, sm, D, L.mu.p, R.prev.p, m.mixes.p);
+                TRY(launch_dep(wkv_mix_kernel, dim3(T), dim3(nt), 0, m.h.p, sm, D, L.mu.p, R.prev.p, m.mixes.p));
                 LAUNCHED();
-                wkv_save_prev_kernel<<<E, nt, 0, g_stream>>>(m.h.p, sm, D, R.prev.p);
+                TRY(launch_dep(wkv_save_prev_kernel, dim3(E), dim3(nt), 0, m.h.p, sm, D, R.prev.p));
                 LAUNCHED();
                 TRY(gemm(m, m.mixes.p + 0 * TD, D, L.r, pr, C, T, C, D));
                 TRY(gemm(m, m.mixes.p + 1 * TD, D, L.k, pk, C, T, C, D));
@@ -704,21 +725,21 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.w0 = L.w0; a.u = L.u;
             a.state = R.state.p; a.out = m.att.p; a.heads = L.d.heads; a.dim = d;
             const dim3 grid(E, L.d.heads);
-            if (d == 32) wkv_scan_split_kernel<32, 8, 4><<<dim3(E, L.d.heads, 1), 128, 0, g_stream>>>(a, sm);
-            else if (d == 64) wkv_scan_split_kernel<64, 8, 8><<<dim3(E, L.d.heads, 2), 256, 0, g_stream>>>(a, sm);
-            else if (d == 128) wkv_scan_split_kernel<128, 4, 16><<<dim3(E, L.d.heads, 4), 512, 0, g_stream>>>(a, sm);
+            if (d == 32) TRY(launch_dep(wkv_scan_split_kernel<32, 8, 4>, dim3(E, L.d.heads, 1), dim3(128), 0, a, sm));
+            else if (d == 64) TRY(launch_dep(wkv_scan_split_kernel<64, 8, 8>, dim3(E, L.d.heads, 2), dim3(256), 0, a, sm));
+            else if (d == 128) TRY(launch_dep(wkv_scan_split_kernel<128, 4, 16>, dim3(E, L.d.heads, 4), dim3(512), 0, a, sm));
             else {
                 const size_t small = 4 * (size_t)d * sizeof(float), full = small + (size_t)d * d * sizeof(float);
                 a.s_in_smem = full <= g_smem_optin ? 1 : 0;
-                wkv_scan_kernel<<<grid, (d + 31) / 32 * 32, a.s_in_smem ? full : small, g_stream>>>(a, sm);
+                TRY(launch_dep(wkv_scan_kernel, dim3(grid), dim3((d + 31) / 32 * 32), a.s_in_smem ? full : small, a, sm));
             }
             LAUNCHED();
-            wkv_finish_kernel<<<(T * L.d.heads + 7) / 8, 256, 0, g_stream>>>(m.att.p, pg, L.normw, T, L.d.heads, d, eps);
+            TRY(launch_dep(wkv_finish_kernel, dim3((T * L.d.heads + 7) / 8), dim3(256), 0, m.att.p, pg, L.normw, T, L.d.heads, d, eps));
             LAUNCHED();
             TRY(gemm(m, m.att.p, C, L.o, m.mo.p, D, T, D, C));
         }
         if (L.d.ff > 0) {
-            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm1b, eps, fuse_rows ? nullptr : L.norm2, m.h.p);
+            TRY(launch_dep(postnorm_residual_kernel, dim3(T), dim3(nt), 0, m.x.p, m.mo.p, D, L.norm1b, eps, fuse_rows ? nullptr : L.norm2, m.h.p));
             LAUNCHED();
             const int F = L.d.ff;
             if (fuse_rows) {   // norm -> [gate | up] -> act(gate) * up in one launch
@@ -731,10 +752,10 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 LAUNCHED();
             }
             TRY(gemm(m, m.act.p, F, L.down, m.mo.p, D, T, D, F));
-            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm2b, eps, nullptr, nullptr);
+            TRY(launch_dep(postnorm_residual_kernel, dim3(T), dim3(nt), 0, m.x.p, m.mo.p, D, L.norm2b, eps, nullptr, nullptr));
             LAUNCHED();
         } else {
-            postnorm_residual_kernel<<<T, nt, 0, g_stream>>>(m.x.p, m.mo.p, D, L.norm1b, eps, nullptr, nullptr);
+            TRY(launch_dep(postnorm_residual_kernel, dim3(T), dim3(nt), 0, m.x.p, m.mo.p, D, L.norm1b, eps, nullptr, nullptr));
             LAUNCHED();
         }
         if (m.dbg) CK(cudaMemcpyAsync(m.dbg_buf.p + ri * (size_t)T * D, m.x.p, (size_t)T * D * sizeof(float), cudaMemcpyDeviceToDevice, g_stream));
@@ -742,13 +763,13 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     m.dbg_rows = T;
     if (n_out > 0) {
         if (few_rows(n_out, D)) {
-            gather_rows_kernel<<<n_out, nt, 0, g_stream>>>(m.x.p, d_out, D, m.hn.p);
+            TRY(launch_dep(gather_rows_kernel, dim3(n_out), dim3(nt), 0, m.x.p, d_out, D, m.hn.p));
             LAUNCHED();
             Fuse f;
             f.norm_gain = m.final_norm; f.eps = eps;
             TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale, &f));
         } else {
-            scalar_rmsnorm_kernel<<<n_out, nt, 0, g_stream>>>(m.x.p, d_out, D, m.final_norm, eps, m.hn.p);
+            TRY(launch_dep(scalar_rmsnorm_kernel, dim3(n_out), dim3(nt), 0, m.x.p, d_out, D, m.final_norm, eps, m.hn.p));
             LAUNCHED();
             TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale));
         }
@@ -756,7 +777,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     if (smp.on) {
         const bool greedy = !(smp.temperature > 0.f) || smp.top_k == 1;
         if (greedy) {
-            argmax_rows_kernel<<<E, 1024, 0, g_stream>>>(m.logits.p, V, V, m.picks.p, m.logprobs.p);
+            TRY(launch_dep(argmax_rows_kernel, dim3(E), dim3(1024), 0, m.logits.p, V, V, m.picks.p, m.logprobs.p));
             LAUNCHED();
         } else {
             const size_t row_smem = sample_row_smem_bytes(V);

@@ -54,7 +54,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // x[t] = embed[tok[t]]; x0 (optional) keeps the embedding output for the looped block's input projection
 template <typename WT>
 __global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, float* x0) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int t = blockIdx.x;
     const WT* e = emb + (size_t)m.tok[t] * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
@@ -65,7 +66,8 @@ __global__ void embed_rows_kernel(const WT* emb, StepMeta m, int D, float* x, fl
 }
 // xc[t] = [x[t]; x0[t]]
 __global__ void concat_rows_kernel(const float* x, const float* x0, int D, float* xc) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int t = blockIdx.x;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         xc[(size_t)t * 2 * D + d] = x[(size_t)t * D + d];
@@ -76,7 +78,8 @@ __global__ void concat_rows_kernel(const float* x, const float* x0, int D, float
 // ---- RMS norm with one gain for all coordinates ----------------------------------------------------------------------
 // y[t] = x[row(t)] / sqrt(mean(x^2) + eps) * gain[0]; rows (optional) gathers (the rows whose logits are wanted)
 __global__ void scalar_rmsnorm_kernel(const float* x, const int* rows, int D, const float* gain, float eps, float* y) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     __shared__ float red[32];
     const int t = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[t] : t) * D;
@@ -89,7 +92,8 @@ __global__ void scalar_rmsnorm_kernel(const float* x, const int* rows, int D, co
 // x[t] += m[t] / sqrt(mean(m^2) + eps) * gain[0]   (the norm behind a sublayer, then the residual sum);
 // with gain2 != null it also writes the next sublayer's input y[t] = x[t] / rms(x[t]) * gain2[0]
 __global__ void postnorm_residual_kernel(float* x, const float* mo, int D, const float* gain, float eps, const float* gain2, float* y) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     __shared__ float red[32];
     const int t = blockIdx.x;
     const float* mr = mo + (size_t)t * D;
@@ -446,7 +450,8 @@ struct AttnShape {
 // Rotation of q and k, unit RMS per head, and the cache append: one block per row.  q is rewritten in place; k and v go
 // to the row's page.  inv_freq[rot_dims / 2] holds the (scaled) frequencies; the angle is position * frequency in fp32.
 __global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const float* inv_freq, float* k_pool, float* v_pool) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int t = blockIdx.x;
     const int pos = m.row_pos[t];
     const int slot = m.ent_slot[m.row_ent[t]];
@@ -494,7 +499,8 @@ constexpr int kAttnWarps = 4;
 constexpr int kAttnMaxPerLane = 8;   // head sizes up to 256
 __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const float* qkvg, StepMeta m, AttnShape s, const int* rows,
                                                                             const float* k_pool, const float* v_pool, float* out) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     extern __shared__ float sm[];   // [kAttnWarps][dv] partial outputs, then [kAttnWarps] max, [kAttnWarps] sum
     const int t = rows ? rows[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -732,7 +738,8 @@ __global__ void glu_kernel(const float* gu, int ff, int act, float* y, size_t n)
 // saved row for an entry's first row, zeros at position 0.
 __global__ void wkv_mix_kernel(const float* h, StepMeta m, int D, const float* mu /*[5][D]*/, const float* prev_state /*[slots][D]*/,
                                float* mixes /*[5][T][D]*/) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int t = blockIdx.x;
     const int e = m.row_ent[t];
     const bool first = (t == m.ent_row0[e]);
@@ -746,7 +753,8 @@ __global__ void wkv_mix_kernel(const float* h, StepMeta m, int D, const float* m
 }
 // the slot keeps the mixer input of the entry's last row for the next step
 __global__ void wkv_save_prev_kernel(const float* h, StepMeta m, int D, float* prev_state) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int e = blockIdx.x;
     const int t = m.ent_row0[e + 1] - 1;
     for (int d = threadIdx.x; d < D; d += blockDim.x) prev_state[(size_t)m.ent_slot[e] * D + d] = h[(size_t)t * D + d];
@@ -765,7 +773,8 @@ struct WkvArgs {
 };
 // any head size: S in shared memory while the entry's rows run (in global memory directly when it does not fit)
 __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     extern __shared__ float sm[];
     const int e = blockIdx.x, hd = blockIdx.y, d = a.dim, j = threadIdx.x;
     const int C = a.heads * d;
@@ -818,7 +827,8 @@ __global__ void wkv_scan_kernel(WkvArgs a, StepMeta m) {
 // are summed (in warp order, so the result does not depend on timing) while the next chunk is staged.  Two block barriers a chunk.
 template <int D, int CH, int NW>
 __global__ void __launch_bounds__(32 * NW) wkv_scan_split_kernel(WkvArgs a, StepMeta m) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     constexpr int RP = D / NW;          // key channels a warp owns
     constexpr int NT = 32 * NW;
     constexpr int PER = CH * D / NT;    // operands of each kind a thread stages per chunk
@@ -920,7 +930,8 @@ __global__ void __launch_bounds__(32 * NW) wkv_scan_split_kernel(WkvArgs a, Step
 }
 // o[t, head] / rms(o[t, head]) * normw * gate, in place: one warp per (row, head)
 __global__ void wkv_finish_kernel(float* o, const float* gate, const float* normw, int T, int heads, int d, float eps) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= T * heads) return;
     const int hd = warp % heads;
@@ -934,7 +945,8 @@ __global__ void wkv_finish_kernel(float* o, const float* gate, const float* norm
 
 // ---- helpers -----------------------------------------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const float* x, const int* rows, int D, float* y) {
-    pdl_launch_dependents();   // a few-row product behind this kernel may start fetching its weights
+    pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
+    pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int t = blockIdx.x;
     for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = x[(size_t)rows[t] * D + d];
 }
