@@ -36,8 +36,10 @@ def main(argv=None) -> int:
         for e in msg.get("entries", []):
             if e["id"] not in live:
                 live[e["id"]] = model.open()
-            entries.append((live[e["id"]], e["tokens"]))
-            want.append(e.get("want", []))
+            if not e.get("tokens"):
+                continue   # admitted, nothing to run for it in this step
+            entries.append((live[e["id"]], [int(t) for t in e["tokens"]]))
+            want.append([int(w) for w in (e.get("want") or [])])
         if entries:
             logits = model.step(entries, want)
             if logits.shape[0]:
