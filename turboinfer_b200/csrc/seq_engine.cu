@@ -35,6 +35,7 @@ bool g_use_tiled_attn = true;   // TURBOINFER_B200_SEQ_TILED_ATTN=0: every row g
 constexpr int kAttnTiledMinRows = 8;
 constexpr int kAttnMaxSplits = 16;    // key chunks of a decode row's attention   // portions at least this long are cut into attention tiles
 bool g_use_pdl = true;  // TURBOINFER_B200_SEQ_PDL=0: the few-row products wait for their predecessor before they start (A/B measurements)
+bool g_use_row_mma = true;   // TURBOINFER_B200_SEQ_ROW_MMA=0: few-row products stay on the fp32 multiply-add kernel (A/B measurements)
 bool g_use_tc = true;   // TURBOINFER_B200_SEQ_TC=0: prompt-side products stay on the warp-level tensor path (A/B measurements)
 
 int fail(const char* fmt, ...) {
@@ -406,6 +407,30 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
         const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, (200u << 10) / std::max<size_t>(xs_bytes, 1)));
         const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * per_sm));
         const Fuse f = fuse ? *fuse : Fuse{};
+        // bf16 weights with K in whole 32-element chunks: the tensor-core form (a weight byte costs the same for 1 and for 8 rows)
+        const size_t mma_bytes = gemv_mma_smem_bytes(M, K);
+        if (m.d.mode == TI_SEQ_BF16 && g_use_row_mma && K % 32 == 0 && K >= 256 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 && mma_bytes <= g_smem_optin) {
+            const int fit = (int)std::max<size_t>(1, std::min<size_t>(2, (200u << 10) / mma_bytes));
+            const int blocks = std::max(1, std::min((N + kMmaCols - 1) / kMmaCols, g_num_sms * fit));
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(blocks);
+            cfg.blockDim = dim3(256);
+            cfg.dynamicSmemBytes = mma_bytes;
+            cfg.stream = g_stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = g_use_pdl ? 1 : 0;
+            if (f.glu_ff > 0)
+                CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<true>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
+                                      f.glu_act));
+            else
+                CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<false>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
+                                      f.glu_act));
+            LAUNCHED();
+            return 0;
+        }
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(kRowGemvThreads);
@@ -851,12 +876,15 @@ int ti_seq_init(int device) {
     g_smem_optin = std::min<size_t>(p.sharedMemPerBlockOptin, 200 * 1024);
     if (!g_stream) CK(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(gemv_rows_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(gemv_rows_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(wkv_front_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(wkv_front_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemv_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgSmemBytes));
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TC")) g_use_tc = atoi(e) != 0;
     if (const char* e = getenv("TURBOINFER_B200_SEQ_PDL")) g_use_pdl = atoi(e) != 0;
+    if (const char* e = getenv("TURBOINFER_B200_SEQ_ROW_MMA")) g_use_row_mma = atoi(e) != 0;
     if (const char* e = getenv("TURBOINFER_B200_SEQ_TILED_ATTN")) g_use_tiled_attn = atoi(e) != 0;
     CK(cudaFuncSetAttribute(window_attention_h3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_h3_smem_bytes<64>()));
     CK(cudaFuncSetAttribute(window_attention_h3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_h3_smem_bytes<128>()));

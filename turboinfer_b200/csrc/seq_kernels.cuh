@@ -382,6 +382,117 @@ __global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const flo
     }
 }
 
+// The same few-row product on the warp-level tensor cores (bf16 weights, bf16-rounded rows, fp32 accumulators): the cost of a
+// weight byte no longer grows with the number of rows.  A block owns 16 output columns, its 8 warps split K; a lane (g = lane / 4,
+// t = lane % 4) reads 16 bytes of column g and of column g + 8 straight from global memory and 16 bytes of row g from shared
+// memory at the same 8 consecutive k -- the k order inside an m16n8k16 step is permuted the same way for both operands, which
+// a dot product does not mind -- and issues two MMAs per 32 k.  The warps' partial tiles are summed through shared memory in warp
+// order.  Needs K % 32 == 0 and 16-byte aligned weight rows.  Row stride in shared memory: K + 32 elements (rows of a quarter
+// warp fall into different banks).
+constexpr int kMmaCols = 16;
+__host__ __device__ inline size_t gemv_mma_smem_bytes(int M, int K) { return (size_t)M * (K + 32) * 2 + 8 * 2 * 128 * sizeof(float); }
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <bool GLU>
+__global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int lda, const __nv_bfloat16* W, float* C, int ldc, int M, int N, int K, int epi,
+                                                           float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int Kp = K + 32;
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smraw);                       // [M][Kp]
+    float* red = reinterpret_cast<float*>(smraw + (size_t)M * Kp * 2);                  // [8 warps][2][128]
+    __shared__ float rss[kRowGemvMaxRows][8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int NC = K / 32, c_begin = warp * NC / 8, c_end = (warp + 1) * NC / 8;   // this warp's 32-k chunks
+    pdl_launch_dependents();
+    {   // ask L2 for this warp's slice of the block's first 16 (32 with the gate's partner) weight rows
+        const int n = min((int)blockIdx.x * kMmaCols + (lane & 15), N - 1);
+        const char* w = reinterpret_cast<const char*>(W + (size_t)n * K + (size_t)c_begin * 32);
+        const size_t bytes = (size_t)(c_end - c_begin) * 64;
+        for (size_t o = (size_t)(lane >> 4) * 128; o < bytes; o += 256) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(w + o));
+            if (GLU) asm volatile("prefetch.global.L2 [%0];" ::"l"(w + o + (size_t)glu_ff * K * 2));
+        }
+    }
+    pdl_wait_prior_grid();
+    // rows -> shared memory as bf16, behind the scalar-gain RMS norm when one is fused in front
+    if (norm_gain) {
+        for (int r = 0; r < M; ++r) {
+            const float* ar = A + (size_t)r * lda;
+            float ss = 0.f;
+            for (int k = threadIdx.x; k < K; k += blockDim.x) ss += ar[k] * ar[k];
+            ss = warp_sum(ss);
+            if (lane == 0) rss[r][warp] = ss;
+        }
+        __syncthreads();
+    }
+    for (int r = 0; r < M; ++r) {
+        float sc = 1.f;
+        if (norm_gain) {
+            float ss = 0.f;
+            for (int w = 0; w < 8; ++w) ss += rss[r][w];
+            sc = norm_gain[0] / sqrtf(ss / (float)K + eps);
+        }
+        const float* ar = A + (size_t)r * lda;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) xs[(size_t)r * Kp + k] = __float2bfloat16_rn(ar[k] * sc);
+    }
+    __syncthreads();
+    constexpr int UNR = GLU ? 4 : 8;   // chunks whose weight loads are in flight together (16-byte loads a lane: 2 or 4 a chunk)
+    for (int n0 = blockIdx.x * kMmaCols; n0 < N; n0 += gridDim.x * kMmaCols) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+        const __nv_bfloat16* w0 = W + (size_t)min(n0 + g, N - 1) * K + 8 * t;
+        const __nv_bfloat16* w1 = W + (size_t)min(n0 + g + 8, N - 1) * K + 8 * t;
+        const size_t up = (size_t)glu_ff * K;
+        const __nv_bfloat16* xr = xs + (size_t)g * Kp + 8 * t;
+        for (int c = c_begin; c < c_end; c += UNR) {
+            uint4 ra[UNR], rb[UNR], ua[GLU ? UNR : 1], ub[GLU ? UNR : 1];
+#pragma unroll
+            for (int q = 0; q < UNR; ++q)
+                if (c + q < c_end) {
+                    const int k = (c + q) * 32;
+                    ra[q] = *reinterpret_cast<const uint4*>(w0 + k);
+                    rb[q] = *reinterpret_cast<const uint4*>(w1 + k);
+                    if (GLU) {
+                        ua[q] = *reinterpret_cast<const uint4*>(w0 + up + k);
+                        ub[q] = *reinterpret_cast<const uint4*>(w1 + up + k);
+                    }
+                }
+#pragma unroll
+            for (int q = 0; q < UNR; ++q)
+                if (c + q < c_end) {
+                    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                    if (g < M) x = *reinterpret_cast<const uint4*>(xr + (c + q) * 32);
+                    mma_bf16_16816(acc, ra[q].x, rb[q].x, ra[q].y, rb[q].y, x.x, x.y);
+                    mma_bf16_16816(acc, ra[q].z, rb[q].z, ra[q].w, rb[q].w, x.z, x.w);
+                    if (GLU) {
+                        mma_bf16_16816(acc2, ua[q].x, ub[q].x, ua[q].y, ub[q].y, x.x, x.y);
+                        mma_bf16_16816(acc2, ua[q].z, ub[q].z, ua[q].w, ub[q].w, x.z, x.w);
+                    }
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            red[(warp * 2 + 0) * 128 + lane * 4 + i] = acc[i];
+            if (GLU) red[(warp * 2 + 1) * 128 + lane * 4 + i] = acc2[i];
+        }
+        __syncthreads();
+        if (threadIdx.x < 128) {   // element (tile column j, row r) sits in lane (j % 8) * 4 + r / 2, register (j / 8) * 2 + r % 2
+            const int j = threadIdx.x >> 3, r = threadIdx.x & 7;
+            const int src = (((j & 7) << 2) + (r >> 1)) * 4 + ((j >> 3) << 1) + (r & 1);
+            float v = 0.f, v2 = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                v += red[(w * 2 + 0) * 128 + src];
+                if (GLU) v2 += red[(w * 2 + 1) * 128 + src];
+            }
+            if (r < M && n0 + j < N) C[(size_t)r * ldc + n0 + j] = GLU ? ff_act(v, glu_act) * v2 : epi_apply(v, epi, alpha);
+        }
+        __syncthreads();
+    }
+}
+
 // The five input products of the wkv mixer for few rows in ONE launch: r, k, v, g and the decay's first matrix each read their
 // own token-shift mix x_s = h + (prev - h) * mu_s, so a block works on one of the five products, builds that product's mix of
 // the rows in shared memory (no mixes in global memory) and streams its share of that product's weight rows.
