@@ -101,6 +101,29 @@ def test_tensor_core_attention_path(dim, kv_heads):
     assert rel_err(b, a) < 2e-2
 
 
+@pytest.mark.parametrize("live", [1, 3, 8])
+def test_decode_rows_on_the_tensor_core_product(live):
+    """Widths in whole 32-element chunks send the decode rows' products of bf16 mode through the tensor-core kernel (1, 3 and 8
+    rows a step, a vocabulary and a feed-forward that are no multiples of its 16-column tiles, one inner size -- 264 -- that is
+    not in whole chunks and stays on the multiply-add kernel).  Decoded rows must agree with the same rows run as one prompt."""
+    cfg = make_config([attn_layer(heads=4, kv_heads=2, dim=64, vdim=80, window=40, rot_dims=32, ff=328),
+                       wkv_layer(heads=5, dim=64, rank=8, ff=264)], vocab=101, width=288, loop=(0, 2, 2))
+    W = random_weights(cfg, seed=31)
+    lens = [50, 9, 33, 70, 21, 7, 12, 40][:live]
+    reqs = {"r%d" % i: tokens(n, 101, 60 + i) for i, n in enumerate(lens)}
+    m = build_engine(cfg, W, "bfloat16", max_tokens=sum((n + 63) // 64 * 64 for n in lens), max_seqs=live)
+    alone = {k: whole(m, v) for k, v in reqs.items()}
+    tail = 6
+    sched = [[(k, len(v) - tail) for k, v in reqs.items()]] + [[(k, 1) for k in reqs]] * tail
+    got = run_schedule(m, reqs, sched)
+    m.free()
+    for k, v in reqs.items():
+        want = plain.forward(cfg, W, v)
+        assert rel_err(alone[k], want) < TOL["bfloat16"], k
+        assert rel_err(got[k], want) < TOL["bfloat16"], k
+        assert rel_err(got[k][-tail:], alone[k][-tail:]) < 2e-2, k   # same rounding points, other summation order
+
+
 @pytest.mark.parametrize("sizes", [[2] * 40, [3, 61, 2, 64, 5, 65, 1, 63, 2], [64, 64, 64], [1, 127, 2, 2, 100], [129, 2, 33]])
 def test_portions(sizes):
     W = random_weights(HYBRID, seed=6)
