@@ -417,12 +417,22 @@ __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int 
         }
     }
     pdl_wait_prior_grid();
-    // rows -> shared memory as bf16, behind the scalar-gain RMS norm when one is fused in front
+    // rows -> shared memory as bf16, behind the scalar-gain RMS norm when one is fused in front; 16-byte loads, several in flight
+    // (every block stages all rows, so this prologue is on the critical path of the launch)
+    const bool v4 = (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);   // K is a multiple of 32
     if (norm_gain) {
         for (int r = 0; r < M; ++r) {
             const float* ar = A + (size_t)r * lda;
             float ss = 0.f;
-            for (int k = threadIdx.x; k < K; k += blockDim.x) ss += ar[k] * ar[k];
+            if (v4) {
+#pragma unroll 4
+                for (int k = threadIdx.x * 4; k < K; k += 1024) {
+                    const float4 v = *reinterpret_cast<const float4*>(ar + k);
+                    ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+                }
+            } else {
+                for (int k = threadIdx.x; k < K; k += blockDim.x) ss += ar[k] * ar[k];
+            }
             ss = warp_sum(ss);
             if (lane == 0) rss[r][warp] = ss;
         }
@@ -436,7 +446,20 @@ __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int 
             sc = norm_gain[0] / sqrtf(ss / (float)K + eps);
         }
         const float* ar = A + (size_t)r * lda;
-        for (int k = threadIdx.x; k < K; k += blockDim.x) xs[(size_t)r * Kp + k] = __float2bfloat16_rn(ar[k] * sc);
+        __nv_bfloat16* xr = xs + (size_t)r * Kp;
+        if (v4) {
+#pragma unroll 4
+            for (int k = threadIdx.x * 4; k < K; k += 1024) {
+                const float4 v = *reinterpret_cast<const float4*>(ar + k);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * sc, v.y * sc), hi = __floats2bfloat162_rn(v.z * sc, v.w * sc);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(xr + k) = pk;
+            }
+        } else {
+            for (int k = threadIdx.x; k < K; k += blockDim.x) xr[k] = __float2bfloat16_rn(ar[k] * sc);
+        }
     }
     __syncthreads();
     constexpr int UNR = GLU ? 4 : 8;   // chunks whose weight loads are in flight together (16-byte loads a lane: 2 or 4 a chunk)
@@ -530,10 +553,24 @@ __global__ void __launch_bounds__(kRowGemvThreads, 2) wkv_front_rows_kernel(WkvF
         const bool first = (r == m.ent_row0[e]);
         const float* pr = first ? (m.ent_pos0[e] > 0 ? a.prev + (size_t)m.ent_slot[e] * K : nullptr) : a.h + (size_t)(r - 1) * K;
         const float* hr = a.h + (size_t)r * K;
-        for (int k = threadIdx.x; k < K; k += blockDim.x) {
-            const float hv = hr[k];
-            const float df = (pr ? pr[k] : 0.f) - hv;
-            xs[(size_t)r * K + k] = act_round<WT>(fmaf(df, mu[k], hv));
+        if (K % 4 == 0) {   // (all row bases are 16-byte aligned then: allocations, and rows K floats apart)
+#pragma unroll 2
+            for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
+                const float4 hv = *reinterpret_cast<const float4*>(hr + k), mv = *reinterpret_cast<const float4*>(mu + k);
+                const float4 pv = pr ? *reinterpret_cast<const float4*>(pr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 o;
+                o.x = act_round<WT>(fmaf(pv.x - hv.x, mv.x, hv.x));
+                o.y = act_round<WT>(fmaf(pv.y - hv.y, mv.y, hv.y));
+                o.z = act_round<WT>(fmaf(pv.z - hv.z, mv.z, hv.z));
+                o.w = act_round<WT>(fmaf(pv.w - hv.w, mv.w, hv.w));
+                *reinterpret_cast<float4*>(xs + (size_t)r * K + k) = o;
+            }
+        } else {
+            for (int k = threadIdx.x; k < K; k += blockDim.x) {
+                const float hv = hr[k];
+                const float df = (pr ? pr[k] : 0.f) - hv;
+                xs[(size_t)r * K + k] = act_round<WT>(fmaf(df, mu[k], hv));
+            }
         }
     }
     __syncthreads();
