@@ -23,8 +23,20 @@ extern "C" {
 
 typedef uint64_t ti_seq_model_t;
 
-enum { TI_SEQ_MIXER_ATTENTION = 0, TI_SEQ_MIXER_WKV = 1 };
+enum {
+    TI_SEQ_MIXER_ATTENTION = 0, /* softmax attention over cached keys / values (windowed, grouped, rotary) */
+    TI_SEQ_MIXER_WKV = 1,       /* token-shifted linear recurrence, output read before the state is updated, bonus term */
+    TI_SEQ_MIXER_GLA = 2,       /* gated linear attention: S <- diag(a) S + k v^T, o = S^T q, a = sigmoid(.)^(1/tau) per key channel */
+    TI_SEQ_MIXER_HGRN2 = 3,     /* the same recurrence with the forget gate f as decay and 1 - f as the written key */
+    TI_SEQ_MIXER_LATENT = 4     /* softmax attention whose keys / values are linear images of a cached low-rank vector + one shared rotated key part */
+};
 enum { TI_SEQ_ACT_RELU = 0, TI_SEQ_ACT_SILU = 1, TI_SEQ_ACT_GELU_TANH = 2 };
+enum {
+    TI_SEQ_FF_GLU = 0,      /* down(act(gate h) * up h) */
+    TI_SEQ_FF_POLYNORM = 1, /* down(a N(z) + b N(z^2) + c N(z^3) + e), z = up h, N = division by the RMS over the inner size */
+    TI_SEQ_FF_EXPERTS = 2   /* routed gated experts (+ identity experts, + a shared expert) */
+};
+enum { TI_SEQ_NORM_SCALAR = 0 /* one gain for all coordinates */, TI_SEQ_NORM_ONE_PLUS = 1 /* per-coordinate gain stored as w, applied as 1 + w */ };
 enum { TI_SEQ_BF16 = 0, TI_SEQ_F32 = 1 };   /* compute mode of a model, and element type of a tensor handed to set_tensor */
 
 typedef struct ti_seq_layer_desc {
@@ -42,6 +54,21 @@ typedef struct ti_seq_layer_desc {
     int32_t decay_rank;      /* wkv: inner size of the decay's two-matrix projection */
     int32_t ff;              /* feed-forward inner size, 0 = the layer has no feed-forward */
     int32_t ff_act;          /* TI_SEQ_ACT_* of the gate branch */
+    /* -- gated linear recurrences (gla, hgrn2): heads, dim (key channels), vdim (value channels) above -- */
+    float decay_tau;         /* gla: decay = sigmoid(z)^(1 / tau); its two-matrix projection has inner size decay_rank */
+    /* -- latent attention: dim = unrotated query/key size, rot_dims = rotated part (one key part shared by the heads), vdim -- */
+    int32_t kv_rank;         /* size of the cached low-rank vector */
+    int32_t kv_from;         /* -1: the layer projects and caches its own; j: it reads layer j's cache (j before this layer) */
+    int32_t sink;            /* 1: the softmax denominator has one more term exp(sink[head]) without key or value */
+    /* -- feed-forward -- */
+    int32_t ff_kind;         /* TI_SEQ_FF_*; `ff` is the inner size of the dense forms and of one routed expert */
+    int32_t experts;         /* routed experts with weights */
+    int32_t identity;        /* router outputs behind them whose expert returns its input */
+    int32_t top;             /* experts a token uses */
+    int32_t groups, groups_keep; /* experts (identity included) form `groups` equal groups of neighbours; only the best `groups_keep` can be chosen */
+    int32_t shared_ff;       /* inner size of the expert every token uses, scaled by a sigmoid of one more projection; 0 = none */
+    /* -- around the sublayers -- */
+    int32_t res_gate;        /* 1: every sublayer's result is multiplied by sigmoid(R h + b) of its input before the norm behind it */
 } ti_seq_layer_desc;
 
 typedef struct ti_seq_model_desc {
@@ -53,6 +80,10 @@ typedef struct ti_seq_model_desc {
     int32_t mode;            /* TI_SEQ_BF16 / TI_SEQ_F32 */
     int32_t max_tokens;      /* tokens the page pool holds (each sequence's count rounds up to whole pages) */
     int32_t max_seqs;        /* state slots = sequences that can be live at once */
+    int32_t norm_kind;       /* TI_SEQ_NORM_* of the norms around the sublayers and in front of the head */
+    float logit_softcap;     /* > 0: logits <- cap * tanh(logits / cap) */
+    int32_t side_dim;        /* > 0: after every layer a per-token side input is added: side.embed[token][layer * side_dim ...] gated by
+                                gelu_tanh(side.gate x), projected back and RMS-normed with a plain per-coordinate weight */
 } ti_seq_model_desc;
 
 int ti_seq_init(int device);
@@ -60,7 +91,8 @@ const char* ti_seq_last_error(void);
 uint64_t ti_seq_launch_count(void);
 
 int ti_seq_model_new(const ti_seq_model_desc* desc, const ti_seq_layer_desc* layers, ti_seq_model_t* out);
-/* tensor names: "embed", "loop.in", "final.norm", "head", "l<i>.norm1|norm1b|norm2|norm2b", "l<i>.mix.<x>", "l<i>.mlp.<x>";
+/* tensor names: "embed", "side.embed", "loop.in", "final.norm", "head", "l<i>.norm1|norm1b|norm2|norm2b", "l<i>.rg1|rg2[.b]",
+ * "l<i>.mix.<x>", "l<i>.mlp.<x>", "l<i>.side.<x>";
  * `dtype` is the element type of `data` (TI_SEQ_BF16: raw bfloat16 bits, TI_SEQ_F32) */
 int ti_seq_model_set_tensor(ti_seq_model_t m, const char* name, int32_t dtype, const void* data, const int64_t* shape, int32_t ndim);
 /* uniform(-amp, amp) + offset generated on the device from (seed, element index): benchmark-size models */

@@ -176,6 +176,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) window_attention_h3_kernel(cons
 // ---- decode rows with long windows: key chunks in parallel -----------------------------------------------------------------
 // grid (rows, heads, splits): split z of a (row, head) takes keys lo + z * chunk .. and leaves its partial (max, sum, o[dv]) in
 // `part`; attention_merge_kernel combines the splits and applies the gate.  chunk = ceil(visible keys / splits).
+template <int PL>
 __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel(const float* qkvg, StepMeta m, AttnShape s, const int* rows, int splits,
                                                                                   const float* k_pool, const float* v_pool, float* part) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
@@ -187,9 +188,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
     const int* table = m.page_table + (size_t)m.ent_slot[m.row_ent[t]] * m.table_stride;
     const int g = h / (s.heads / s.kv_heads);
     const float* q = qkvg + (size_t)t * s.ld + (size_t)h * s.dim;
-    float qr[kAttnMaxPerLane], o[kAttnMaxPerLane];
+    float qr[PL], o[PL];
 #pragma unroll
-    for (int i = 0; i < kAttnMaxPerLane; ++i) {
+    for (int i = 0; i < PL; ++i) {
         const int d = lane + 32 * i;
         qr[i] = d < s.dim ? q[d] : 0.f;
         o[i] = 0.f;
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
     const int chunk = (pos - lo + 1 + splits - 1) / splits;
     const int j0 = lo + z * chunk, j1 = min(pos, j0 + chunk - 1);
     float mx = -INFINITY, l = 0.f;
-    const size_t kstride = (size_t)s.kv_heads * s.dim, vstride = (size_t)s.kv_heads * s.vdim;
+    const size_t kstride = (size_t)s.kv_heads * s.dim, vstride = attn_vstride(s);
     // a warp takes its keys four at a time: the four K rows (and then the four V rows) are requested together
     for (int jb = j0 + 4 * warp; jb <= j1; jb += 4 * kAttnWarps) {
         size_t off[4];
@@ -210,16 +211,16 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
             sc[u] = 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < kAttnMaxPerLane; ++i) {
+        for (int i = 0; i < PL; ++i) {
             const int d = lane + 32 * i;
             if (d < s.dim) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) sc[u] = fmaf(qr[i], k_pool[off[u] * kstride + (size_t)g * s.dim + d], sc[u]);
             }
         }
-        float vv[4][kAttnMaxPerLane];
+        float vv[4][PL];
 #pragma unroll
-        for (int i = 0; i < kAttnMaxPerLane; ++i) {
+        for (int i = 0; i < PL; ++i) {
             const int d = lane + 32 * i;
 #pragma unroll
             for (int u = 0; u < 4; ++u) vv[u][i] = d < s.vdim ? v_pool[off[u] * vstride + (size_t)g * s.vdim + d] : 0.f;
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
                 const float corr = expf(mx - nm), p = expf(su - nm);
                 l = l * corr + p;
 #pragma unroll
-                for (int i = 0; i < kAttnMaxPerLane; ++i) o[i] = fmaf(p, vv[u][i], o[i] * corr);
+                for (int i = 0; i < PL; ++i) o[i] = fmaf(p, vv[u][i], o[i] * corr);
                 mx = nm;
             }
         }
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_split_kernel
     float* pm = sm + kAttnWarps * s.vdim;
     float* pl = pm + kAttnWarps;
 #pragma unroll
-    for (int i = 0; i < kAttnMaxPerLane; ++i) {
+    for (int i = 0; i < PL; ++i) {
         const int d = lane + 32 * i;
         if (d < s.vdim) po[warp * s.vdim + d] = o[i];
     }
@@ -287,6 +288,7 @@ __global__ void attention_merge_kernel(const float* part, const float* qkvg, Ste
         const float zg = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * s.dim + (size_t)s.kv_heads * s.vdim + h];
         gate = 1.f / (1.f + expf(-zg));
     }
+    const float fin = attn_finish_factor(s, h, Mx, L) * gate;
     for (int d0 = 0; d0 < s.vdim; d0 += 32) {
         const int d = d0 + lane;
         float acc = 0.f;
@@ -294,7 +296,7 @@ __global__ void attention_merge_kernel(const float* part, const float* qkvg, Ste
             const float f = __shfl_sync(0xFFFFFFFFu, fz, z);
             if (d < s.vdim) acc = fmaf(p[(size_t)z * ps + 2 + d], f, acc);
         }
-        if (d < s.vdim) out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc / L * gate;
+        if (d < s.vdim) out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc * fin;
     }
 }
 

@@ -19,6 +19,9 @@
 #include "seq_kernels.cuh"
 #include "seq_gemm_tc.cuh"
 #include "seq_attn_tc.cuh"
+#include "seq_recurrent.cuh"
+#include "seq_latent.cuh"
+#include "seq_experts.cuh"
 #include "sampling.cuh"
 
 using namespace tib;
@@ -174,14 +177,33 @@ struct LayerW {
     const void *gateup = nullptr, *down = nullptr;
     DevBuf<uint8_t> gateup_buf;
     const float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr;
+    // gla / hgrn2 / latent attention: ONE fused input projection [q | k or f | v | gate | decay-in | down-kv | residual gate] (the parts
+    // the mixer has), its width and the column where each part starts (-1: the mixer has no such part)
+    const void* front = nullptr;
+    DevBuf<uint8_t> front_buf;
+    int n_front = 0, off_q = -1, off_k = -1, off_v = -1, off_g = -1, off_a1 = -1, off_dkv = -1, off_rg1 = -1;
+    const void *a2 = nullptr, *uv = nullptr;
+    DevBuf<uint8_t> ukT;                       // latent attention: per head the transpose of the key up-projection [heads][rank][dim]
+    const float *a2b = nullptr, *fb = nullptr, *lower = nullptr, *cnorm = nullptr, *sink = nullptr;
+    // feed-forward forms with a fused front [router | shared scale | residual gate | up or experts' gate, up | shared gate, up]
+    const void* ffront = nullptr;
+    DevBuf<uint8_t> ffront_buf, down_buf;      // down_buf: experts' (and the shared expert's) down matrices side by side along K
+    int n_ffront = 0, off_router = -1, off_sg = -1, off_rg2 = -1, off_up = -1, off_sh = -1, ff_width = 0;
+    const float *poly = nullptr, *correction = nullptr;
+    const void *rg1 = nullptr, *rg2 = nullptr; // residual gates that are not part of a fused front (products of their own)
+    const float *rg1b = nullptr, *rg2b = nullptr;
+    // per-token side input
+    const void *side_gate = nullptr, *side_proj = nullptr;
+    const float* side_norm = nullptr;
 };
 
 // one execution of a layer: a looped layer runs several times, every run with its own cache or state
 struct Run {
     int layer = 0;
     bool enters_pass = false;   // the looped block's input projection comes right before this run
-    DevBuf<float> k_pool, v_pool;          // attention: [pages * 64][G * d], [pages * 64][G * dv]
-    DevBuf<float> state, prev;             // wkv: [slots][H][d][d], [slots][D]
+    DevBuf<float> k_pool, v_pool;          // attention: [pages * 64][G * d], [pages * 64][G * dv]; latent attention: k_pool [pages * 64][rank + rot]
+    DevBuf<float> state, prev;             // wkv: [slots][H][d][d], [slots][D]; gla / hgrn2: state [slots][H][dk][dv]
+    int kv_run = -1;                       // latent attention reading another layer's cache: the run that owns it
 };
 
 struct SeqState {
@@ -198,8 +220,9 @@ struct Model {
     std::vector<std::string> order;   // required tensors in a fixed order
     bool finalized = false;
     size_t wsize = 2;                 // bytes per matrix element
-    const void *embed = nullptr, *loop_in = nullptr, *head = nullptr;
+    const void *embed = nullptr, *loop_in = nullptr, *head = nullptr, *side_embed = nullptr;
     const float* final_norm = nullptr;
+    int gvec = 0;                     // 1: the norms around the sublayers have one gain per coordinate
     // cache manager
     int num_pages = 0;
     std::vector<int> free_pages;
@@ -207,6 +230,9 @@ struct Model {
     // step scratch
     int cap_rows = 0, cap_want = 0;
     DevBuf<float> x, x0, xc, h, proj, mixes, att, mo, act, lora, hn, logits, logprobs;
+    DevBuf<float> aux, aux2, route, rgbuf;   // decays / absorbed queries, weighted latent sums, routing weights, unfused residual gates
+    int max_aux = 0, max_aux2 = 0, max_route = 0;
+    bool any_rgbuf = false;
     DevBuf<int> meta, picks;
     DevBuf<__nv_bfloat16> abf;   // bf16 copy of a product's activations for the tcgen05 path: [rows][max_k]
     DevBuf<float> attn_part;     // split-key attention partials: [rows][heads][splits][vdim + 2]
@@ -245,15 +271,19 @@ void require(Model& m, const std::string& name, std::vector<int64_t> shape, bool
     m.order.push_back(name);
 }
 
+bool is_recurrent(int mixer) { return mixer == TI_SEQ_MIXER_WKV || mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2; }
+
 int describe_tensors(Model& m) {
     const int64_t D = m.d.width, V = m.d.vocab;
+    const std::vector<int64_t> gain_shape = m.d.norm_kind == TI_SEQ_NORM_ONE_PLUS ? std::vector<int64_t>{D} : std::vector<int64_t>{};
     require(m, "embed", {V, D}, true);
+    if (m.d.side_dim > 0) require(m, "side.embed", {V, (int64_t)m.d.side_dim * m.d.n_layers}, true);
     if (m.d.loop_times > 0) require(m, "loop.in", {D, 2 * D}, true);
     for (int i = 0; i < m.d.n_layers; ++i) {
         const ti_seq_layer_desc& L = m.layers[i].d;
         const std::string p = "l" + std::to_string(i) + ".";
-        require(m, p + "norm1", {}, false);
-        require(m, p + "norm1b", {}, false);
+        require(m, p + "norm1", gain_shape, false);
+        require(m, p + "norm1b", gain_shape, false);
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
             if (L.heads <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) return fail("layer %d: heads %d / kv_heads %d", i, L.heads, L.kv_heads);
             if (L.dim <= 0 || L.vdim <= 0 || L.dim > 32 * kAttnMaxPerLane || L.vdim > 32 * kAttnMaxPerLane)
@@ -275,18 +305,97 @@ int describe_tensors(Model& m) {
             require(m, p + "mix.u", {(int64_t)L.heads, (int64_t)L.dim}, false);
             require(m, p + "mix.norm", {C}, false);
             require(m, p + "mix.o", {D, C}, true);
+        } else if (L.mixer == TI_SEQ_MIXER_GLA || L.mixer == TI_SEQ_MIXER_HGRN2) {
+            if (L.heads <= 0 || L.dim <= 0 || L.vdim <= 0 || L.dim > 4096 || L.vdim > 65535 * 128)
+                return fail("layer %d: recurrence heads %d dim %d vdim %d", i, L.heads, L.dim, L.vdim);
+            const int64_t C = (int64_t)L.heads * L.dim, Cv = (int64_t)L.heads * L.vdim;
+            require(m, p + "mix.q", {C, D}, true);
+            if (L.mixer == TI_SEQ_MIXER_GLA) {
+                if (L.decay_rank <= 0 || !(L.decay_tau > 0.f)) return fail("layer %d: gla decay rank %d tau %g", i, L.decay_rank, L.decay_tau);
+                require(m, p + "mix.k", {C, D}, true);
+                require(m, p + "mix.v", {Cv, D}, true);
+                require(m, p + "mix.g", {Cv, D}, true);
+                require(m, p + "mix.a1", {(int64_t)L.decay_rank, D}, true);
+                require(m, p + "mix.a2", {C, (int64_t)L.decay_rank}, true);
+                require(m, p + "mix.a2.b", {C}, false);
+            } else {
+                require(m, p + "mix.f", {C, D}, true);
+                require(m, p + "mix.f.b", {C}, false);
+                require(m, p + "mix.lower", {C}, false);
+                require(m, p + "mix.v", {Cv, D}, true);
+            }
+            require(m, p + "mix.norm", {(int64_t)L.vdim}, false);
+            require(m, p + "mix.o", {D, Cv}, true);
+        } else if (L.mixer == TI_SEQ_MIXER_LATENT) {
+            if (L.heads <= 0 || L.dim <= 0 || L.vdim <= 0 || L.kv_rank <= 0 || L.rot_dims < 0 || (L.rot_dims & 1))
+                return fail("layer %d: latent attention heads %d dim %d rot %d vdim %d rank %d", i, L.heads, L.dim, L.rot_dims, L.vdim, L.kv_rank);
+            if (L.kv_rank + L.rot_dims > 32 * kAttnWidePerLane) return fail("layer %d: cached row of %d + %d exceeds %d", i, L.kv_rank, L.rot_dims, 32 * kAttnWidePerLane);
+            if (L.kv_from >= 0) {
+                if (L.kv_from >= i) return fail("layer %d: reads the cache of layer %d, which does not run before it", i, L.kv_from);
+                const ti_seq_layer_desc& S = m.layers[L.kv_from].d;
+                if (S.mixer != TI_SEQ_MIXER_LATENT || S.kv_from >= 0 || S.kv_rank != L.kv_rank || S.rot_dims != L.rot_dims || S.rot_base != L.rot_base)
+                    return fail("layer %d: layer %d has no cache of its own with the same rank, rotated size and rotation", i, L.kv_from);
+            }
+            require(m, p + "mix.q", {(int64_t)L.heads * (L.dim + L.rot_dims), D}, true);
+            if (L.kv_from < 0) {
+                require(m, p + "mix.dkv", {(int64_t)L.kv_rank + L.rot_dims, D}, true);
+                require(m, p + "mix.dkv.norm", {(int64_t)L.kv_rank}, false);
+            }
+            require(m, p + "mix.uk", {(int64_t)L.heads * L.dim, (int64_t)L.kv_rank}, true);
+            require(m, p + "mix.uv", {(int64_t)L.heads * L.vdim, (int64_t)L.kv_rank}, true);
+            if (L.sink) require(m, p + "mix.sink", {(int64_t)L.heads}, false);
+            require(m, p + "mix.o", {D, (int64_t)L.heads * L.vdim}, true);
         } else {
             return fail("layer %d: unknown mixer %d", i, L.mixer);
         }
+        if (L.res_gate) {
+            require(m, p + "rg1", {D, D}, true);
+            require(m, p + "rg1.b", {D}, false);
+        }
         if (L.ff > 0) {
-            require(m, p + "norm2", {}, false);
-            require(m, p + "norm2b", {}, false);
-            require(m, p + "mlp.gate", {(int64_t)L.ff, D}, true);
-            require(m, p + "mlp.up", {(int64_t)L.ff, D}, true);
-            require(m, p + "mlp.down", {D, (int64_t)L.ff}, true);
+            require(m, p + "norm2", gain_shape, false);
+            require(m, p + "norm2b", gain_shape, false);
+            if (L.ff_kind == TI_SEQ_FF_GLU) {
+                require(m, p + "mlp.gate", {(int64_t)L.ff, D}, true);
+                require(m, p + "mlp.up", {(int64_t)L.ff, D}, true);
+                require(m, p + "mlp.down", {D, (int64_t)L.ff}, true);
+            } else if (L.ff_kind == TI_SEQ_FF_POLYNORM) {
+                require(m, p + "mlp.up", {(int64_t)L.ff, D}, true);
+                require(m, p + "mlp.down", {D, (int64_t)L.ff}, true);
+                require(m, p + "mlp.act", {4}, false);
+            } else if (L.ff_kind == TI_SEQ_FF_EXPERTS) {
+                const int n = L.experts + L.identity;
+                if (L.experts < 0 || L.identity < 0 || n <= 0 || L.top <= 0 || L.top > n || L.groups <= 0 || n % L.groups || L.groups_keep <= 0 || L.groups_keep > L.groups)
+                    return fail("layer %d: %d experts + %d identity, top %d, %d groups keep %d", i, L.experts, L.identity, L.top, L.groups, L.groups_keep);
+                for (int e = 0; e < L.experts; ++e) {
+                    const std::string q = p + "mlp.e" + std::to_string(e) + ".";
+                    require(m, q + "gate", {(int64_t)L.ff, D}, true);
+                    require(m, q + "up", {(int64_t)L.ff, D}, true);
+                    require(m, q + "down", {D, (int64_t)L.ff}, true);
+                }
+                require(m, p + "mlp.router", {(int64_t)n, D}, true);
+                require(m, p + "mlp.correction", {(int64_t)n}, false);
+                if (L.shared_ff > 0) {
+                    require(m, p + "mlp.shared.gate", {(int64_t)L.shared_ff, D}, true);
+                    require(m, p + "mlp.shared.up", {(int64_t)L.shared_ff, D}, true);
+                    require(m, p + "mlp.shared.down", {D, (int64_t)L.shared_ff}, true);
+                    require(m, p + "mlp.shared.sg", {1, D}, true);
+                }
+            } else {
+                return fail("layer %d: unknown feed-forward kind %d", i, L.ff_kind);
+            }
+            if (L.res_gate) {
+                require(m, p + "rg2", {D, D}, true);
+                require(m, p + "rg2.b", {D}, false);
+            }
+        }
+        if (m.d.side_dim > 0) {
+            require(m, p + "side.gate", {(int64_t)m.d.side_dim, D}, true);
+            require(m, p + "side.proj", {D, (int64_t)m.d.side_dim}, true);
+            require(m, p + "side.norm", {D}, false);
         }
     }
-    require(m, "final.norm", {}, false);
+    require(m, "final.norm", gain_shape, false);
     require(m, "head", {V, D}, true);
     return 0;
 }
@@ -324,10 +433,11 @@ std::vector<float> rotary_frequencies(const ti_seq_layer_desc& L) {
     return f;
 }
 
-int concat_rows(Model& m, std::initializer_list<const Tensor*> parts, DevBuf<uint8_t>& out, int* rows) {
+int concat_rows(Model& m, const std::vector<const Tensor*>& parts, DevBuf<uint8_t>& out, int* rows, std::vector<int>* offsets = nullptr) {
     size_t bytes = 0;
     int n = 0;
     for (const Tensor* t : parts) {
+        if (offsets) offsets->push_back(t ? n : -1);
         if (!t) continue;
         bytes += t->data.n;
         n += (int)t->shape[0];
@@ -343,6 +453,31 @@ int concat_rows(Model& m, std::initializer_list<const Tensor*> parts, DevBuf<uin
     *rows = n;
     (void)m;
     return 0;
+}
+
+// matrices [rows][cols_i] side by side along the columns: out [rows][sum cols_i]
+int concat_cols(Model& m, const std::vector<const Tensor*>& parts, DevBuf<uint8_t>& out, int* cols) {
+    int64_t rows = -1, total = 0;
+    for (const Tensor* t : parts) {
+        if (!t) continue;
+        if (rows >= 0 && t->shape[0] != rows) return fail("internal: column concatenation of matrices with different row counts");
+        rows = t->shape[0];
+        total += t->shape[1];
+    }
+    TRY(out.alloc((size_t)rows * total * m.wsize));
+    size_t off = 0;
+    for (const Tensor* t : parts) {
+        if (!t) continue;
+        const size_t w = (size_t)t->shape[1] * m.wsize;
+        CK(cudaMemcpy2DAsync(out.p + off, (size_t)total * m.wsize, t->data.p, w, w, (size_t)rows, cudaMemcpyDeviceToDevice, g_stream));
+        off += w;
+    }
+    CK(cudaStreamSynchronize(g_stream));
+    *cols = (int)total;
+    return 0;
+}
+__global__ void add_one_kernel(float* w, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) w[i] += 1.f;
 }
 
 // ---- tensor maps for the tcgen05 path: a bf16 matrix [rows][cols], cols contiguous, boxes of 64 x 128 with the 128-byte swizzle ----
@@ -390,7 +525,8 @@ int launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&
 }
 
 struct Fuse {
-    const float* norm_gain = nullptr;   // scalar-gain RMS norm of the input rows in front of the product
+    const float* norm_gain = nullptr;   // RMS norm of the input rows in front of the product (gvec: one gain per coordinate)
+    int gvec = 0;
     float eps = 0.f;
     int glu_ff = 0, glu_act = 0;        // act(gate) * up behind a fused [gate | up] product: N is then the inner size
 };
@@ -424,10 +560,10 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
             cfg.numAttrs = g_use_pdl ? 1 : 0;
             if (f.glu_ff > 0)
                 CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<true>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
-                                      f.glu_act));
+                                      f.glu_act, f.gvec));
             else
                 CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<false>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
-                                      f.glu_act));
+                                      f.glu_act, f.gvec));
             LAUNCHED();
             return 0;
         }
@@ -443,10 +579,10 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
         cfg.numAttrs = g_use_pdl ? 1 : 0;
         if (m.d.mode == TI_SEQ_BF16)
             CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<__nv_bfloat16>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps,
-                                  f.glu_ff, f.glu_act));
+                                  f.glu_ff, f.glu_act, f.gvec));
         else
             CK(cudaLaunchKernelEx(&cfg, gemv_rows_kernel<float>, A, lda, (const float*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
-                                  f.glu_act));
+                                  f.glu_act, f.gvec));
         LAUNCHED();
         return 0;
     }
@@ -485,6 +621,10 @@ int ensure_scratch(Model& m, int rows, int want) {
         TRY(m.mo.alloc(R * D));
         if (m.max_ff) TRY(m.act.alloc(R * (size_t)m.max_ff));
         if (m.max_rank) TRY(m.lora.alloc(R * (size_t)m.max_rank));
+        if (m.max_aux) TRY(m.aux.alloc(R * (size_t)m.max_aux));
+        if (m.max_aux2) TRY(m.aux2.alloc(R * (size_t)m.max_aux2));
+        if (m.max_route) TRY(m.route.alloc(R * (size_t)m.max_route));
+        if (m.any_rgbuf) TRY(m.rgbuf.alloc(R * D));
         if (m.dbg) TRY(m.dbg_buf.alloc(m.runs.size() * R * D));
         if (m.d.mode == TI_SEQ_BF16 && g_use_tc) TRY(m.abf.alloc(R * (size_t)m.max_k));
         if (m.max_heads_v) TRY(m.attn_part.alloc(R * (size_t)m.max_heads_v * kAttnMaxSplits));
@@ -659,6 +799,60 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     else TRY(launch_dep(embed_rows_kernel<float>, dim3(T), dim3(nt), 0, (const float*)m.embed, sm, D, m.x.p, m.d.loop_times > 0 ? m.x0.p : nullptr));
     LAUNCHED();
     const float eps = m.d.norm_eps;
+    const int gv = m.gvec;
+    const size_t ws = m.wsize;
+    // the end of a sublayer: (identity experts) -> (gate) -> norm behind the sublayer -> residual sum (-> the next sublayer's input)
+    auto post = [&](const float* gain, int gain_vec, const float* gain2, const float* gate, int gate_ld, const float* gate_bias, const float* idw) -> int {
+        PostArgs a{};
+        a.x = m.x.p; a.mo = m.mo.p; a.gain = gain; a.gain2 = gain2; a.y = m.h.p; a.gate = gate; a.gate_bias = gate_bias; a.idw = idw; a.hin = m.h.p;
+        a.gate_ld = gate_ld; a.D = D; a.gvec = gain_vec; a.gvec2 = gv; a.eps = eps;
+        TRY(launch_dep(postnorm_residual_kernel, dim3(T), dim3(nt), 0, a));
+        LAUNCHED();
+        return 0;
+    };
+    // paged softmax attention of all rows of the step (prompt portions in tiles, the other rows one by one or split over their keys)
+    auto attention = [&](const AttnShape& s, const float* q, const float* kp, const float* vp, float* out) -> int {
+        const bool wide = std::max(s.dim, s.vdim) > 32 * kAttnMaxPerLane;
+        const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
+        const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim);
+        const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && tsmem <= g_smem_optin && (s.v_ld % 4 == 0);
+        // bf16 mode, head sizes 64 / 128: the split-half tensor-core kernel (fp32-accurate); fp32 mode keeps true fp32 arithmetic
+        const bool h3_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles128 > 0 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
+                           (s.kv_heads * s.dim) % 4 == 0 && !s.sink && s.v_ld == 0;
+        const int* rest = (tiled_ok || h3_ok) ? d_small : nullptr;
+        const int n_rest = (tiled_ok || h3_ok) ? n_small : T;
+        if (h3_ok) {
+            const dim3 grid(n_tiles128, s.heads);
+            if (s.dim == 64) window_attention_h3_kernel<64><<<grid, kTcThreads, attn_h3_smem_bytes<64>(), g_stream>>>(q, sm, s, d_tiles128, kp, vp, out);
+            else window_attention_h3_kernel<128><<<grid, kTcThreads, attn_h3_smem_bytes<128>(), g_stream>>>(q, sm, s, d_tiles128, kp, vp, out);
+            LAUNCHED();
+        } else if (tiled_ok) {
+            const dim3 grid(n_tiles, s.heads);
+            if (s.vdim <= 64) window_attention_tiled_kernel<1><<<grid, 256, tsmem, g_stream>>>(q, sm, s, d_tiles, kp, vp, out);
+            else if (s.vdim <= 128) window_attention_tiled_kernel<2><<<grid, 256, tsmem, g_stream>>>(q, sm, s, d_tiles, kp, vp, out);
+            else if (s.vdim <= 256) window_attention_tiled_kernel<4><<<grid, 256, tsmem, g_stream>>>(q, sm, s, d_tiles, kp, vp, out);
+            else window_attention_tiled_kernel<8><<<grid, 256, tsmem, g_stream>>>(q, sm, s, d_tiles, kp, vp, out);
+            LAUNCHED();
+        }
+        if (n_rest > 0) {
+            // single rows: key chunks in parallel (a row-at-a-time walk is one memory round trip a key) unless the rows alone fill the GPU
+            const int span = s.window > 0 ? std::min(s.window, max_pos + 1) : max_pos + 1;
+            int splits = 1;
+            if (span >= 32) splits = std::max(1, std::min({(span + 15) / 16, kAttnMaxSplits, (2 * g_num_sms) / std::max(1, n_rest * s.heads)}));
+            if (splits > 1 && m.attn_part.p) {
+                if (wide) TRY(launch_dep(window_attention_split_kernel<kAttnWidePerLane>, dim3(n_rest, s.heads, splits), dim3(kAttnWarps * 32), smem, q, sm, s, rest, splits, kp, vp, m.attn_part.p));
+                else TRY(launch_dep(window_attention_split_kernel<kAttnMaxPerLane>, dim3(n_rest, s.heads, splits), dim3(kAttnWarps * 32), smem, q, sm, s, rest, splits, kp, vp, m.attn_part.p));
+                LAUNCHED();
+                TRY(launch_dep(attention_merge_kernel, dim3((n_rest * s.heads + 7) / 8), dim3(256), 0, (const float*)m.attn_part.p, q, sm, s, rest, n_rest, splits, out));
+                LAUNCHED();
+            } else {
+                if (wide) TRY(launch_dep(window_attention_kernel<kAttnWidePerLane>, dim3(n_rest, s.heads), dim3(kAttnWarps * 32), smem, q, sm, s, rest, kp, vp, out));
+                else TRY(launch_dep(window_attention_kernel<kAttnMaxPerLane>, dim3(n_rest, s.heads), dim3(kAttnWarps * 32), smem, q, sm, s, rest, kp, vp, out));
+                LAUNCHED();
+            }
+        }
+        return 0;
+    };
     for (size_t ri = 0; ri < m.runs.size(); ++ri) {
         Run& R = m.runs[ri];
         LayerW& L = m.layers[R.layer];
@@ -667,12 +861,23 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             LAUNCHED();
             TRY(gemm(m, m.xc.p, 2 * D, m.loop_in, m.x.p, D, T, D, 2 * D));
         }
+        const int mixer = L.d.mixer;
+        const bool attn = mixer == TI_SEQ_MIXER_ATTENTION;
         // decode steps (few rows) fuse the norm in front of the attention projections into the product's prologue
-        const bool fuse_rows = few_rows(T, D);
-        const bool attn = L.d.mixer == TI_SEQ_MIXER_ATTENTION;
+        const bool fuse_rows = few_rows(T, D) && !L.d.res_gate;
         if (!(fuse_rows && attn)) {
-            TRY(launch_dep(scalar_rmsnorm_kernel, dim3(T), dim3(nt), 0, m.x.p, nullptr, D, L.norm1, eps, m.h.p));
+            TRY(launch_dep(rmsnorm_kernel, dim3(T), dim3(nt), 0, (const float*)m.x.p, (const int*)nullptr, D, L.norm1, gv, eps, m.h.p));
             LAUNCHED();
+        }
+        const float* gate1 = nullptr;   // residual gate of the mixer: pre-activations and their row stride
+        int gate1_ld = 0;
+        if (L.d.res_gate && L.rg1) {
+            TRY(gemm(m, m.h.p, D, L.rg1, m.rgbuf.p, D, T, D, D));
+            gate1 = m.rgbuf.p;
+            gate1_ld = D;
+        } else if (L.d.res_gate) {
+            gate1 = m.proj.p + L.off_rg1;
+            gate1_ld = L.n_front;
         }
         if (attn) {
             AttnShape s{};
@@ -681,51 +886,16 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             s.scale = L.d.scale; s.eps = eps; s.ld = L.n_qkvg;
             if (fuse_rows) {
                 Fuse f;
-                f.norm_gain = L.norm1; f.eps = eps;
+                f.norm_gain = L.norm1; f.eps = eps; f.gvec = gv;
                 TRY(gemm(m, m.x.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D, EPI_NONE, 1.f, &f));
             } else {
                 TRY(gemm(m, m.h.p, D, L.qkvg, m.proj.p, L.n_qkvg, T, L.n_qkvg, D));
             }
             TRY(launch_dep(attn_prepare_kernel, dim3(T), dim3(128), 0, m.proj.p, sm, s, L.inv_freq.p, R.k_pool.p, R.v_pool.p));
             LAUNCHED();
-            const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
-            const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim);
-            const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && tsmem <= g_smem_optin;
-            // bf16 mode, head sizes 64 / 128: the split-half tensor-core kernel (fp32-accurate); fp32 mode keeps true fp32 arithmetic
-            const bool h3_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles128 > 0 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
-                               (s.kv_heads * s.dim) % 4 == 0;
-            const int* rest = (tiled_ok || h3_ok) ? d_small : nullptr;
-            const int n_rest = (tiled_ok || h3_ok) ? n_small : T;
-            if (h3_ok) {
-                const dim3 grid(n_tiles128, s.heads);
-                if (s.dim == 64) window_attention_h3_kernel<64><<<grid, kTcThreads, attn_h3_smem_bytes<64>(), g_stream>>>(m.proj.p, sm, s, d_tiles128, R.k_pool.p, R.v_pool.p, m.att.p);
-                else window_attention_h3_kernel<128><<<grid, kTcThreads, attn_h3_smem_bytes<128>(), g_stream>>>(m.proj.p, sm, s, d_tiles128, R.k_pool.p, R.v_pool.p, m.att.p);
-                LAUNCHED();
-            } else if (tiled_ok) {
-                const dim3 grid(n_tiles, s.heads);
-                if (s.vdim <= 64) window_attention_tiled_kernel<1><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
-                else if (s.vdim <= 128) window_attention_tiled_kernel<2><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
-                else window_attention_tiled_kernel<4><<<grid, 256, tsmem, g_stream>>>(m.proj.p, sm, s, d_tiles, R.k_pool.p, R.v_pool.p, m.att.p);
-                LAUNCHED();
-            }
-            if (n_rest > 0) {
-                // single rows: key chunks in parallel (a row-at-a-time walk is one memory round trip a key) unless the rows alone fill the GPU
-                const int span = s.window > 0 ? std::min(s.window, max_pos + 1) : max_pos + 1;
-                int splits = 1;
-                if (span >= 32) splits = std::max(1, std::min({(span + 15) / 16, kAttnMaxSplits, (2 * g_num_sms) / std::max(1, n_rest * s.heads)}));
-                if (splits > 1 && m.attn_part.p) {
-                    TRY(launch_dep(window_attention_split_kernel, dim3(n_rest, s.heads, splits), dim3(kAttnWarps * 32), smem, m.proj.p, sm, s, rest, splits, R.k_pool.p,
-                                                                                                                        R.v_pool.p, m.attn_part.p));
-                    LAUNCHED();
-                    TRY(launch_dep(attention_merge_kernel, dim3((n_rest * s.heads + 7) / 8), dim3(256), 0, m.attn_part.p, m.proj.p, sm, s, rest, n_rest, splits, m.att.p));
-                    LAUNCHED();
-                } else {
-                    TRY(launch_dep(window_attention_kernel, dim3(n_rest, s.heads), dim3(kAttnWarps * 32), smem, m.proj.p, sm, s, rest, R.k_pool.p, R.v_pool.p, m.att.p));
-                    LAUNCHED();
-                }
-            }
+            TRY(attention(s, m.proj.p, R.k_pool.p, R.v_pool.p, m.att.p));
             TRY(gemm(m, m.att.p, s.heads * s.vdim, L.o, m.mo.p, D, T, D, s.heads * s.vdim));
-        } else {
+        } else if (mixer == TI_SEQ_MIXER_WKV) {
             const int C = L.d.heads * L.d.dim, d = L.d.dim, rank = L.d.decay_rank;
             const size_t TD = (size_t)T * D, TC = (size_t)T * C;
             float *pr = m.proj.p, *pk = pr + TC, *pv = pk + TC, *pg = pv + TC, *pz = pg + TC;
@@ -759,44 +929,146 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 TRY(launch_dep(wkv_scan_kernel, dim3(grid), dim3((d + 31) / 32 * 32), a.s_in_smem ? full : small, a, sm));
             }
             LAUNCHED();
-            TRY(launch_dep(wkv_finish_kernel, dim3((T * L.d.heads + 7) / 8), dim3(256), 0, m.att.p, pg, L.normw, T, L.d.heads, d, eps));
+            TRY(launch_dep(head_rmsnorm_gate_kernel, dim3((T * L.d.heads + 7) / 8), dim3(256), 0, m.att.p, (const float*)pg, C, 0, L.normw, 1, T, L.d.heads, d, eps));
             LAUNCHED();
             TRY(gemm(m, m.att.p, C, L.o, m.mo.p, D, T, D, C));
+        } else if (mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2) {
+            const bool gla = mixer == TI_SEQ_MIXER_GLA;
+            const int H = L.d.heads, dk = L.d.dim, dv = L.d.vdim, C = H * dk, Cv = H * dv, nf = L.n_front;
+            TRY(gemm(m, m.h.p, D, L.front, m.proj.p, nf, T, nf, D));
+            LinScanArgs a{};
+            a.q = m.proj.p + L.off_q; a.ldq = nf;
+            a.v = m.proj.p + L.off_v; a.ldv = nf;
+            if (gla) {   // decay = sigmoid(A2 (A1 h) + b)^(1 / tau)
+                TRY(gemm(m, m.proj.p + L.off_a1, nf, L.a2, m.aux.p, C, T, C, L.d.decay_rank));
+                TRY(launch_dep(gla_decay_kernel, dim3(grid_for((size_t)T * C)), dim3(256), 0, m.aux.p, L.a2b, 1.f / L.d.decay_tau, C, (size_t)T * C));
+                LAUNCHED();
+                a.k = m.proj.p + L.off_k; a.ldk = nf;
+                a.a = m.aux.p; a.lda = C;
+                a.qscale = 1.f / sqrtf((float)dk);
+            } else {     // q = silu(.), forget gate f = lower + (1 - lower) sigmoid(. + b) is the decay, 1 - f is written
+                TRY(launch_dep(hgrn2_gates_kernel, dim3(grid_for((size_t)T * C)), dim3(256), 0, m.proj.p, nf, L.off_q, L.off_k, L.fb, L.lower, C, T));
+                LAUNCHED();
+                a.k = nullptr; a.ldk = 0;
+                a.a = m.proj.p + L.off_k; a.lda = nf;
+                a.qscale = 1.f;
+            }
+            a.state = R.state.p; a.out = m.att.p; a.heads = H; a.dk = dk; a.dv = dv;
+            const int threads = std::min(128, (dv + 31) / 32 * 32);
+            const dim3 grid(E, H, (dv + threads - 1) / threads);
+            if (dk <= 32) TRY(launch_dep(linear_scan_kernel<32>, grid, dim3(threads), linear_scan_smem_bytes(dk, threads, false), a, sm));
+            else if (dk <= 64) TRY(launch_dep(linear_scan_kernel<64>, grid, dim3(threads), linear_scan_smem_bytes(dk, threads, false), a, sm));
+            else if (dk <= 128) TRY(launch_dep(linear_scan_kernel<128>, grid, dim3(threads), linear_scan_smem_bytes(dk, threads, false), a, sm));
+            else {
+                const int th = linear_scan_smem_bytes(dk, threads, true) <= g_smem_optin ? threads : 32;
+                const dim3 g2(E, H, (dv + th - 1) / th);
+                if (linear_scan_smem_bytes(dk, th, true) > g_smem_optin) return fail("layer %d: %d key channels do not fit the recurrence kernel", R.layer, dk);
+                TRY(launch_dep(linear_scan_kernel<0>, g2, dim3(th), linear_scan_smem_bytes(dk, th, true), a, sm));
+            }
+            LAUNCHED();
+            TRY(launch_dep(head_rmsnorm_gate_kernel, dim3((T * H + 7) / 8), dim3(256), 0, m.att.p, gla ? (const float*)(m.proj.p + L.off_g) : (const float*)nullptr, nf, 1,
+                           L.normw, 0, T, H, dv, eps));
+            LAUNCHED();
+            TRY(gemm(m, m.att.p, Cv, L.o, m.mo.p, D, T, D, Cv));
+        } else {   // latent attention
+            const int H = L.d.heads, d = L.d.dim, dr = L.d.rot_dims, dv = L.d.vdim, rank = L.d.kv_rank, kd = rank + dr, nf = L.n_front;
+            TRY(gemm(m, m.h.p, D, L.front, m.proj.p, nf, T, nf, D));
+            float* pool = R.kv_run >= 0 ? m.runs[R.kv_run].k_pool.p : R.k_pool.p;
+            LatentShape ls{};
+            ls.heads = H; ls.dim = d; ls.rot = dr; ls.rank = rank; ls.ld = nf; ls.off_q = L.off_q; ls.off_dkv = L.off_dkv; ls.eps = eps;
+            TRY(launch_dep(latent_prepare_kernel, dim3(T), dim3(128), 0, (const float*)m.proj.p, sm, ls, (const float*)L.inv_freq.p, L.cnorm, pool, m.aux.p));
+            LAUNCHED();
+            // the key up-projection moves to the query: qabs[t][h][0 .. rank) = Uk_h^T q_h
+            for (int h = 0; h < H; ++h)
+                TRY(gemm(m, m.proj.p + L.off_q + (size_t)h * (d + dr), nf, L.ukT.p + (size_t)h * rank * d * ws, m.aux.p + (size_t)h * kd, H * kd, T, rank, d));
+            AttnShape s{};
+            s.heads = H; s.kv_heads = 1; s.dim = kd; s.vdim = rank; s.window = 0; s.rot_dims = 0; s.qk_norm = 0; s.out_gate = 0;
+            s.scale = L.d.scale; s.eps = eps; s.ld = H * kd; s.v_ld = kd; s.sink = L.sink;
+            TRY(attention(s, m.aux.p, pool, pool, m.aux2.p));
+            // ... and the value up-projection behind the weighted sum: att[t][h] = Uv_h (sum_j p_j c_j)
+            for (int h = 0; h < H; ++h)
+                TRY(gemm(m, m.aux2.p + (size_t)h * rank, H * rank, (const uint8_t*)L.uv + (size_t)h * dv * rank * ws, m.att.p + (size_t)h * dv, H * dv, T, dv, rank));
+            TRY(gemm(m, m.att.p, H * dv, L.o, m.mo.p, D, T, D, H * dv));
         }
         if (L.d.ff > 0) {
-            TRY(launch_dep(postnorm_residual_kernel, dim3(T), dim3(nt), 0, m.x.p, m.mo.p, D, L.norm1b, eps, fuse_rows ? nullptr : L.norm2, m.h.p));
-            LAUNCHED();
-            const int F = L.d.ff;
-            if (fuse_rows) {   // norm -> [gate | up] -> act(gate) * up in one launch
-                Fuse f;
-                f.norm_gain = L.norm2; f.eps = eps; f.glu_ff = F; f.glu_act = L.d.ff_act;
-                TRY(gemm(m, m.x.p, D, L.gateup, m.act.p, F, T, F, D, EPI_NONE, 1.f, &f));
-            } else {
-                TRY(gemm(m, m.h.p, D, L.gateup, m.proj.p, 2 * F, T, 2 * F, D));
-                glu_kernel<<<grid_for((size_t)T * F), 256, 0, g_stream>>>(m.proj.p, F, L.d.ff_act, m.act.p, (size_t)T * F);
-                LAUNCHED();
+            const bool fuse_ff = fuse_rows && L.d.ff_kind == TI_SEQ_FF_GLU;
+            TRY(post(L.norm1b, gv, fuse_ff ? nullptr : L.norm2, gate1, gate1_ld, L.rg1b, nullptr));
+            const float* gate2 = nullptr;
+            int gate2_ld = 0;
+            if (L.d.res_gate && L.rg2) {
+                TRY(gemm(m, m.h.p, D, L.rg2, m.rgbuf.p, D, T, D, D));
+                gate2 = m.rgbuf.p;
+                gate2_ld = D;
+            } else if (L.d.res_gate) {
+                gate2 = m.proj.p + L.off_rg2;
+                gate2_ld = L.n_ffront;
             }
-            TRY(gemm(m, m.act.p, F, L.down, m.mo.p, D, T, D, F));
-            TRY(launch_dep(postnorm_residual_kernel, dim3(T), dim3(nt), 0, m.x.p, m.mo.p, D, L.norm2b, eps, nullptr, nullptr));
-            LAUNCHED();
+            const float* idw = nullptr;
+            const int F = L.d.ff;
+            if (L.d.ff_kind == TI_SEQ_FF_GLU) {
+                if (fuse_ff) {   // norm -> [gate | up] -> act(gate) * up in one launch
+                    Fuse f;
+                    f.norm_gain = L.norm2; f.eps = eps; f.gvec = gv; f.glu_ff = F; f.glu_act = L.d.ff_act;
+                    TRY(gemm(m, m.x.p, D, L.gateup, m.act.p, F, T, F, D, EPI_NONE, 1.f, &f));
+                } else {
+                    TRY(gemm(m, m.h.p, D, L.gateup, m.proj.p, 2 * F, T, 2 * F, D));
+                    glu_kernel<<<grid_for((size_t)T * F), 256, 0, g_stream>>>(m.proj.p, F, L.d.ff_act, m.act.p, (size_t)T * F);
+                    LAUNCHED();
+                }
+            } else if (L.d.ff_kind == TI_SEQ_FF_POLYNORM) {
+                TRY(gemm(m, m.h.p, D, L.ffront, m.proj.p, L.n_ffront, T, L.n_ffront, D));
+                TRY(launch_dep(polynorm_kernel, dim3(T), dim3(nt), 0, (const float*)(m.proj.p + L.off_up), L.n_ffront, F, L.poly, eps, m.act.p));
+                LAUNCHED();
+            } else {
+                const int nfw = L.n_ffront, Ex = L.d.experts;
+                TRY(gemm(m, m.h.p, D, L.ffront, m.proj.p, nfw, T, nfw, D));
+                RouteShape r{};
+                r.n_real = Ex; r.n_id = L.d.identity; r.top = L.d.top; r.groups = L.d.groups; r.keep = L.d.groups_keep;
+                float* wdense = m.route.p;
+                float* idw_buf = m.route.p + (size_t)T * std::max(Ex, 1);
+                const int rw = 4;
+                const size_t rsm = (size_t)rw * (2 * (Ex + L.d.identity) + L.d.groups) * sizeof(float);
+                TRY(launch_dep(moe_route_kernel, dim3((T + rw - 1) / rw), dim3(rw * 32), rsm, (const float*)m.proj.p, nfw, L.off_router, r, L.correction, T, wdense, idw_buf));
+                LAUNCHED();
+                if (L.ff_width > 0) {
+                    TRY(launch_dep(moe_act_kernel, dim3(grid_for((size_t)T * L.ff_width)), dim3(256), 0, (const float*)m.proj.p, nfw, L.off_up, Ex, F, (const float*)wdense, L.off_sh,
+                                   L.d.shared_ff, L.off_sg, m.act.p, T));
+                    LAUNCHED();
+                }
+                if (L.d.identity > 0) idw = idw_buf;
+            }
+            if (L.ff_width > 0) TRY(gemm(m, m.act.p, L.ff_width, L.down, m.mo.p, D, T, D, L.ff_width));
+            else CK(cudaMemsetAsync(m.mo.p, 0, (size_t)T * D * sizeof(float), g_stream));
+            TRY(post(L.norm2b, gv, nullptr, gate2, gate2_ld, L.rg2b, idw));
         } else {
-            TRY(launch_dep(postnorm_residual_kernel, dim3(T), dim3(nt), 0, m.x.p, m.mo.p, D, L.norm1b, eps, nullptr, nullptr));
+            TRY(post(L.norm1b, gv, nullptr, gate1, gate1_ld, L.rg1b, nullptr));
+        }
+        if (m.d.side_dim > 0) {   // per-token side input: x += plain_norm(P (gelu_tanh(G x) * side_embedding[token, layer slice]))
+            const int ds = m.d.side_dim;
+            TRY(gemm(m, m.x.p, D, L.side_gate, m.aux2.p, ds, T, ds, D, EPI_GELU_TANH));
+            if (bf) TRY(launch_dep(side_mul_kernel<__nv_bfloat16>, dim3(grid_for((size_t)T * ds)), dim3(256), 0, m.aux2.p, sm, (const __nv_bfloat16*)m.side_embed, ds * m.d.n_layers, R.layer, ds));
+            else TRY(launch_dep(side_mul_kernel<float>, dim3(grid_for((size_t)T * ds)), dim3(256), 0, m.aux2.p, sm, (const float*)m.side_embed, ds * m.d.n_layers, R.layer, ds));
             LAUNCHED();
+            TRY(gemm(m, m.aux2.p, ds, L.side_proj, m.mo.p, D, T, D, ds));
+            TRY(post(L.side_norm, 1, nullptr, nullptr, 0, nullptr, nullptr));
         }
         if (m.dbg) CK(cudaMemcpyAsync(m.dbg_buf.p + ri * (size_t)T * D, m.x.p, (size_t)T * D * sizeof(float), cudaMemcpyDeviceToDevice, g_stream));
     }
     m.dbg_rows = T;
     if (n_out > 0) {
+        // logits: scaled, or capped through cap * tanh(. / cap)
+        const int head_epi = m.d.logit_softcap > 0.f ? EPI_SOFTCAP : EPI_SCALE;
+        const float head_alpha = m.d.logit_softcap > 0.f ? m.d.logit_softcap : m.d.logit_scale;
         if (few_rows(n_out, D)) {
             TRY(launch_dep(gather_rows_kernel, dim3(n_out), dim3(nt), 0, m.x.p, d_out, D, m.hn.p));
             LAUNCHED();
             Fuse f;
-            f.norm_gain = m.final_norm; f.eps = eps;
-            TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale, &f));
+            f.norm_gain = m.final_norm; f.eps = eps; f.gvec = m.gvec;
+            TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, head_epi, head_alpha, &f));
         } else {
-            TRY(launch_dep(scalar_rmsnorm_kernel, dim3(n_out), dim3(nt), 0, m.x.p, d_out, D, m.final_norm, eps, m.hn.p));
+            TRY(launch_dep(rmsnorm_kernel, dim3(n_out), dim3(nt), 0, (const float*)m.x.p, d_out, D, m.final_norm, m.gvec, eps, m.hn.p));
             LAUNCHED();
-            TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, EPI_SCALE, m.d.logit_scale));
+            TRY(gemm(m, m.hn.p, D, m.head, m.logits.p, V, n_out, V, D, head_epi, head_alpha));
         }
     }
     if (smp.on) {
@@ -892,6 +1164,8 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(window_attention_tiled_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(window_attention_tiled_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(wkv_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(window_attention_tiled_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(linear_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     g_device = device;
@@ -1027,18 +1301,36 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
     const int D = m.d.width;
     m.embed = P("embed");
     m.head = P("head");
-    m.final_norm = F("final.norm");
+    if (m.d.side_dim > 0) m.side_embed = P("side.embed");
     if (m.d.loop_times > 0) m.loop_in = P("loop.in");
+    m.gvec = m.d.norm_kind == TI_SEQ_NORM_ONE_PLUS ? 1 : 0;
+    if (m.gvec) {   // gains stored around zero and applied as 1 + w: converted once
+        std::vector<std::string> names{"final.norm"};
+        for (int i = 0; i < m.d.n_layers; ++i)
+            for (const char* sfx : {"norm1", "norm1b", "norm2", "norm2b"}) names.push_back("l" + std::to_string(i) + "." + sfx);
+        for (const auto& nm : names)
+            if (Tensor* t = T(nm)) {
+                add_one_kernel<<<grid_for(t->count()), 256, 0, g_stream>>>(reinterpret_cast<float*>(t->data.p), t->count());
+                LAUNCHED();
+            }
+        CK(cudaStreamSynchronize(g_stream));
+    }
+    m.final_norm = F("final.norm");
+    m.max_k = 2 * D;
+    auto note_k = [&](int k) { m.max_k = std::max(m.max_k, k); };
+    auto release = [&](const std::string& nm) {
+        if (Tensor* t = T(nm)) t->data.release();
+    };
     for (int i = 0; i < m.d.n_layers; ++i) {
         LayerW& L = m.layers[i];
         const std::string p = "l" + std::to_string(i) + ".";
         L.norm1 = F(p + "norm1");
         L.norm1b = F(p + "norm1b");
+        bool rg1_fused = false, rg2_fused = false;
         if (L.d.mixer == TI_SEQ_MIXER_ATTENTION) {
             TRY(concat_rows(m, {T(p + "mix.q"), T(p + "mix.k"), T(p + "mix.v"), L.d.out_gate ? T(p + "mix.g") : nullptr}, L.qkvg_buf, &L.n_qkvg));
             L.qkvg = L.qkvg_buf.p;
-            for (const char* s : {"mix.q", "mix.k", "mix.v", "mix.g"})
-                if (T(p + s)) T(p + s)->data.release();
+            for (const char* s : {"mix.q", "mix.k", "mix.v", "mix.g"}) release(p + s);
             L.o = P(p + "mix.o");
             const std::vector<float> f = rotary_frequencies(L.d);
             TRY(L.inv_freq.alloc(std::max<size_t>(1, f.size())));
@@ -1046,7 +1338,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             m.max_proj = std::max(m.max_proj, L.n_qkvg);
             m.max_att = std::max(m.max_att, L.d.heads * L.d.vdim);
             m.max_heads_v = std::max(m.max_heads_v, L.d.heads * (L.d.vdim + 2));
-        } else {
+        } else if (L.d.mixer == TI_SEQ_MIXER_WKV) {
             const int C = L.d.heads * L.d.dim;
             L.r = P(p + "mix.r"); L.k = P(p + "mix.k"); L.v = P(p + "mix.v"); L.g = P(p + "mix.g");
             L.w1 = P(p + "mix.w1"); L.w2 = P(p + "mix.w2"); L.o = P(p + "mix.o");
@@ -1059,37 +1351,169 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
             m.max_att = std::max(m.max_att, C);
             m.max_rank = std::max(m.max_rank, L.d.decay_rank);
             m.any_wkv = true;
+        } else if (L.d.mixer == TI_SEQ_MIXER_GLA || L.d.mixer == TI_SEQ_MIXER_HGRN2) {
+            const bool gla = L.d.mixer == TI_SEQ_MIXER_GLA;
+            const int C = L.d.heads * L.d.dim, Cv = L.d.heads * L.d.vdim;
+            std::vector<int> off;
+            TRY(concat_rows(m, {T(p + "mix.q"), T(p + (gla ? "mix.k" : "mix.f")), T(p + "mix.v"), gla ? T(p + "mix.g") : nullptr, gla ? T(p + "mix.a1") : nullptr,
+                                L.d.res_gate ? T(p + "rg1") : nullptr}, L.front_buf, &L.n_front, &off));
+            L.front = L.front_buf.p;
+            L.off_q = off[0]; L.off_k = off[1]; L.off_v = off[2]; L.off_g = off[3]; L.off_a1 = off[4]; L.off_rg1 = off[5];
+            rg1_fused = L.d.res_gate != 0;
+            for (const char* s : {"mix.q", "mix.k", "mix.f", "mix.v", "mix.g", "mix.a1", "rg1"}) release(p + s);
+            if (gla) {
+                L.a2 = P(p + "mix.a2");
+                L.a2b = F(p + "mix.a2.b");
+                note_k(L.d.decay_rank);
+                m.max_aux = std::max(m.max_aux, C);
+            } else {
+                L.fb = F(p + "mix.f.b");
+                L.lower = F(p + "mix.lower");
+            }
+            L.normw = F(p + "mix.norm");
+            L.o = P(p + "mix.o");
+            m.max_proj = std::max(m.max_proj, L.n_front);
+            m.max_att = std::max(m.max_att, Cv);
+        } else {   // latent attention
+            const int H = L.d.heads, kd = L.d.kv_rank + L.d.rot_dims;
+            std::vector<int> off;
+            TRY(concat_rows(m, {T(p + "mix.q"), L.d.kv_from < 0 ? T(p + "mix.dkv") : nullptr, L.d.res_gate ? T(p + "rg1") : nullptr}, L.front_buf, &L.n_front, &off));
+            L.front = L.front_buf.p;
+            L.off_q = off[0]; L.off_dkv = off[1]; L.off_rg1 = off[2];
+            rg1_fused = L.d.res_gate != 0;
+            for (const char* s : {"mix.q", "mix.dkv", "rg1"}) release(p + s);
+            if (L.d.kv_from < 0) L.cnorm = F(p + "mix.dkv.norm");
+            if (L.d.sink) L.sink = F(p + "mix.sink");
+            TRY(L.ukT.alloc((size_t)H * L.d.dim * L.d.kv_rank * m.wsize));
+            const size_t n = (size_t)H * L.d.dim * L.d.kv_rank;
+            if (m.d.mode == TI_SEQ_BF16)
+                transpose_heads_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, g_stream>>>((const __nv_bfloat16*)P(p + "mix.uk"), H, L.d.dim, L.d.kv_rank, (__nv_bfloat16*)L.ukT.p);
+            else
+                transpose_heads_kernel<float><<<grid_for(n), 256, 0, g_stream>>>((const float*)P(p + "mix.uk"), H, L.d.dim, L.d.kv_rank, (float*)L.ukT.p);
+            LAUNCHED();
+            CK(cudaStreamSynchronize(g_stream));
+            release(p + "mix.uk");
+            L.uv = P(p + "mix.uv");
+            L.o = P(p + "mix.o");
+            ti_seq_layer_desc rd = L.d;   // frequencies of the rotated part: every pair of it turns
+            rd.rot_scaled = 0;
+            const std::vector<float> f = rotary_frequencies(rd);
+            TRY(L.inv_freq.alloc(std::max<size_t>(1, f.size())));
+            if (!f.empty()) CK(cudaMemcpy(L.inv_freq.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
+            note_k(L.d.dim);
+            note_k(L.d.kv_rank);
+            m.max_proj = std::max(m.max_proj, L.n_front);
+            m.max_att = std::max(m.max_att, H * L.d.vdim);
+            m.max_aux = std::max(m.max_aux, H * kd);
+            m.max_aux2 = std::max(m.max_aux2, H * L.d.kv_rank);
+            m.max_heads_v = std::max(m.max_heads_v, H * (L.d.kv_rank + 2));
+        }
+        if (L.d.res_gate) {
+            L.rg1b = F(p + "rg1.b");
+            if (!rg1_fused) { L.rg1 = P(p + "rg1"); m.any_rgbuf = true; }
         }
         if (L.d.ff > 0) {
-            int rows = 0;
-            TRY(concat_rows(m, {T(p + "mlp.gate"), T(p + "mlp.up")}, L.gateup_buf, &rows));
-            L.gateup = L.gateup_buf.p;
-            T(p + "mlp.gate")->data.release();
-            T(p + "mlp.up")->data.release();
-            L.down = P(p + "mlp.down");
             L.norm2 = F(p + "norm2");
             L.norm2b = F(p + "norm2b");
-            m.max_proj = std::max(m.max_proj, 2 * L.d.ff);
-            m.max_ff = std::max(m.max_ff, L.d.ff);
+            if (L.d.ff_kind == TI_SEQ_FF_GLU) {
+                int rows = 0;
+                TRY(concat_rows(m, {T(p + "mlp.gate"), T(p + "mlp.up")}, L.gateup_buf, &rows));
+                L.gateup = L.gateup_buf.p;
+                release(p + "mlp.gate");
+                release(p + "mlp.up");
+                L.down = P(p + "mlp.down");
+                L.ff_width = L.d.ff;
+                m.max_proj = std::max(m.max_proj, 2 * L.d.ff);
+            } else if (L.d.ff_kind == TI_SEQ_FF_POLYNORM) {
+                std::vector<int> off;
+                TRY(concat_rows(m, {T(p + "mlp.up"), L.d.res_gate ? T(p + "rg2") : nullptr}, L.ffront_buf, &L.n_ffront, &off));
+                L.ffront = L.ffront_buf.p;
+                L.off_up = off[0]; L.off_rg2 = off[1];
+                rg2_fused = L.d.res_gate != 0;
+                release(p + "mlp.up");
+                release(p + "rg2");
+                L.poly = F(p + "mlp.act");
+                L.down = P(p + "mlp.down");
+                L.ff_width = L.d.ff;
+                m.max_proj = std::max(m.max_proj, L.n_ffront);
+            } else {
+                const int E = L.d.experts;
+                std::vector<const Tensor*> parts{T(p + "mlp.router"), L.d.shared_ff > 0 ? T(p + "mlp.shared.sg") : nullptr, L.d.res_gate ? T(p + "rg2") : nullptr};
+                std::vector<const Tensor*> downs;
+                for (int e = 0; e < E; ++e) {
+                    const std::string q = p + "mlp.e" + std::to_string(e) + ".";
+                    parts.push_back(T(q + "gate"));
+                    parts.push_back(T(q + "up"));
+                    downs.push_back(T(q + "down"));
+                }
+                if (L.d.shared_ff > 0) {
+                    parts.push_back(T(p + "mlp.shared.gate"));
+                    parts.push_back(T(p + "mlp.shared.up"));
+                    downs.push_back(T(p + "mlp.shared.down"));
+                }
+                std::vector<int> off;
+                TRY(concat_rows(m, parts, L.ffront_buf, &L.n_ffront, &off));
+                L.ffront = L.ffront_buf.p;
+                L.off_router = off[0]; L.off_sg = off[1]; L.off_rg2 = off[2];
+                L.off_up = E > 0 ? off[3] : -1;
+                L.off_sh = L.d.shared_ff > 0 ? off[3 + 2 * E] : -1;
+                rg2_fused = L.d.res_gate != 0;
+                L.ff_width = E * L.d.ff + L.d.shared_ff;
+                if (L.ff_width > 0) {
+                    int cols = 0;
+                    TRY(concat_cols(m, downs, L.down_buf, &cols));
+                    L.down = L.down_buf.p;
+                }
+                for (int e = 0; e < E; ++e)
+                    for (const char* s : {"gate", "up", "down"}) release(p + "mlp.e" + std::to_string(e) + "." + s);
+                for (const char* s : {"mlp.router", "mlp.shared.sg", "mlp.shared.gate", "mlp.shared.up", "mlp.shared.down", "rg2"}) release(p + s);
+                L.correction = F(p + "mlp.correction");
+                m.max_proj = std::max(m.max_proj, L.n_ffront);
+                m.max_route = std::max(m.max_route, std::max(E, 1) + 1);
+            }
+            m.max_ff = std::max(m.max_ff, L.ff_width);
+            if (L.d.res_gate) {
+                L.rg2b = F(p + "rg2.b");
+                if (!rg2_fused) { L.rg2 = P(p + "rg2"); m.any_rgbuf = true; }
+            }
+        }
+        if (m.d.side_dim > 0) {
+            L.side_gate = P(p + "side.gate");
+            L.side_proj = P(p + "side.proj");
+            L.side_norm = F(p + "side.norm");
+            m.max_aux2 = std::max(m.max_aux2, m.d.side_dim);
+            note_k(m.d.side_dim);
         }
     }
     // cache pools and state slots: one of each per layer RUN
     m.num_pages = (m.d.max_tokens + kPageTokens - 1) / kPageTokens;
     for (int p = m.num_pages - 1; p >= 0; --p) m.free_pages.push_back(p);
     m.seqs.resize(m.d.max_seqs);
-    for (Run& R : m.runs) {
+    for (size_t ri = 0; ri < m.runs.size(); ++ri) {
+        Run& R = m.runs[ri];
         const ti_seq_layer_desc& L = m.layers[R.layer].d;
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
             TRY(R.k_pool.alloc((size_t)m.num_pages * kPageTokens * L.kv_heads * L.dim));
             TRY(R.v_pool.alloc((size_t)m.num_pages * kPageTokens * L.kv_heads * L.vdim));
-        } else {
+        } else if (L.mixer == TI_SEQ_MIXER_LATENT) {
+            if (L.kv_from < 0) {
+                TRY(R.k_pool.alloc((size_t)m.num_pages * kPageTokens * (L.kv_rank + L.rot_dims)));
+            } else {   // the latest earlier run of the layer whose cache this one reads
+                for (size_t rj = 0; rj < ri; ++rj)
+                    if (m.runs[rj].layer == L.kv_from) R.kv_run = (int)rj;
+                if (R.kv_run < 0) return fail("finalize: layer %d reads the cache of layer %d, which has not run before it", R.layer, L.kv_from);
+            }
+        } else if (L.mixer == TI_SEQ_MIXER_WKV) {
             TRY(R.state.alloc((size_t)m.d.max_seqs * L.heads * L.dim * L.dim));
             TRY(R.prev.alloc((size_t)m.d.max_seqs * D));
             CK(cudaMemset(R.state.p, 0, R.state.n * sizeof(float)));
             CK(cudaMemset(R.prev.p, 0, R.prev.n * sizeof(float)));
+        } else {
+            TRY(R.state.alloc((size_t)m.d.max_seqs * L.heads * L.dim * L.vdim));
+            CK(cudaMemset(R.state.p, 0, R.state.n * sizeof(float)));
         }
     }
-    m.max_k = std::max({2 * D, m.max_att, m.max_ff, m.max_rank, D});
+    m.max_k = std::max({m.max_k, 2 * D, m.max_att, m.max_ff, m.max_rank, D});
     TRY(m.err.alloc(1));
     CK(cudaMemset(m.err.p, 0, sizeof(int)));
     CK(cudaEventCreate(&m.ev0));
@@ -1288,12 +1712,31 @@ int ti_seq_model_bytes(ti_seq_model_t h, double* weight_bytes, double* kv_bytes_
         if (L.mixer == TI_SEQ_MIXER_ATTENTION) {
             w += ((double)L.heads * L.dim + (double)L.kv_heads * (L.dim + L.vdim) + (L.out_gate ? L.heads : 0) + (double)L.heads * L.vdim) * D * ws;
             kv += (double)L.kv_heads * (L.dim + L.vdim) * 4;
-        } else {
+        } else if (L.mixer == TI_SEQ_MIXER_WKV) {
             const double C = (double)L.heads * L.dim;
             w += (5 * C * D + (double)L.decay_rank * (D + C)) * ws;
             st += ((double)L.heads * L.dim * L.dim + D) * 4;
+        } else if (L.mixer == TI_SEQ_MIXER_GLA || L.mixer == TI_SEQ_MIXER_HGRN2) {
+            const double C = (double)L.heads * L.dim, Cv = (double)L.heads * L.vdim;
+            w += (2 * C * D + 2 * Cv * D) * ws;   // q, k or f, v, o
+            if (L.mixer == TI_SEQ_MIXER_GLA) w += (Cv * D + (double)L.decay_rank * (D + C)) * ws;
+            st += (double)L.heads * L.dim * L.vdim * 4;
+        } else {
+            const double H = L.heads;
+            w += (H * (L.dim + L.rot_dims) * D + H * (L.dim + L.vdim) * L.kv_rank + H * L.vdim * D) * ws;
+            if (L.kv_from < 0) {
+                w += (double)(L.kv_rank + L.rot_dims) * D * ws;
+                kv += (double)(L.kv_rank + L.rot_dims) * 4;
+            }
         }
-        if (L.ff > 0) w += 3.0 * L.ff * D * ws;
+        if (L.res_gate) w += (L.ff > 0 ? 2.0 : 1.0) * D * D * ws;
+        if (L.ff > 0) {
+            // routed experts: the stacked products read every expert's weights whatever the tokens chose
+            if (L.ff_kind == TI_SEQ_FF_GLU) w += 3.0 * L.ff * D * ws;
+            else if (L.ff_kind == TI_SEQ_FF_POLYNORM) w += 2.0 * L.ff * D * ws;
+            else w += (3.0 * ((double)L.experts * L.ff + L.shared_ff) + L.experts + L.identity + (L.shared_ff > 0 ? 1 : 0)) * D * ws;
+        }
+        if (m->d.side_dim > 0) w += 2.0 * m->d.side_dim * D * ws;
     }
     w += (double)m->d.vocab * D * ws;
     if (weight_bytes) *weight_bytes = w;

@@ -75,9 +75,11 @@ __global__ void concat_rows_kernel(const float* x, const float* x0, int D, float
     }
 }
 
-// ---- RMS norm with one gain for all coordinates ----------------------------------------------------------------------
-// y[t] = x[row(t)] / sqrt(mean(x^2) + eps) * gain[0]; rows (optional) gathers (the rows whose logits are wanted)
-__global__ void scalar_rmsnorm_kernel(const float* x, const int* rows, int D, const float* gain, float eps, float* y) {
+// ---- RMS norms -------------------------------------------------------------------------------------------------------------
+// The gain is one number for all coordinates (gvec = 0: gain[0]) or one per coordinate (gvec = 1: gain[d]; a design that stores
+// its gains around zero and applies 1 + w has them converted once when the model is finalized).
+// y[t] = x[row(t)] / sqrt(mean(x^2) + eps) * gain; rows (optional) gathers (the rows whose logits are wanted)
+__global__ void rmsnorm_kernel(const float* x, const int* rows, int D, const float* gain, int gvec, float eps, float* y) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
     pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     __shared__ float red[32];
@@ -86,41 +88,70 @@ __global__ void scalar_rmsnorm_kernel(const float* x, const int* rows, int D, co
     float ss = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) ss += xr[d] * xr[d];
     ss = block_sum(ss, red);
-    const float sc = gain[0] / sqrtf(ss / (float)D + eps);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = xr[d] * sc;
+    const float sc = 1.f / sqrtf(ss / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = xr[d] * sc * gain[gvec ? d : 0];
 }
-// x[t] += m[t] / sqrt(mean(m^2) + eps) * gain[0]   (the norm behind a sublayer, then the residual sum);
-// with gain2 != null it also writes the next sublayer's input y[t] = x[t] / rms(x[t]) * gain2[0]
-__global__ void postnorm_residual_kernel(float* x, const float* mo, int D, const float* gain, float eps, const float* gain2, float* y) {
+// The end of a sublayer: x[t] += norm(m[t]) with m = the sublayer's result, optionally
+//   * multiplied first by sigmoid(gate[t][d] + gate_bias[d]) (a gated residual: `gate` is a slice of the sublayer's fused input
+//     projection, row stride gate_ld), and
+//   * with idw[t] * hin[t][d] added before that (experts that return their input, weighted by the router),
+// and with gain2 != null the next sublayer's input y[t] = x[t] / rms(x[t]) * gain2 is written in the same pass.
+struct PostArgs {
+    float* x;              // [T][D] residual stream, updated in place
+    float* mo;             // [T][D] sublayer result (overwritten with the gated value when a gate is given)
+    const float* gain;     // norm behind the sublayer
+    const float* gain2;    // norm in front of the next sublayer (null: none)
+    float* y;              // [T][D] next sublayer's input
+    const float* gate;     // null: no gate
+    const float* gate_bias;
+    const float* idw;      // [T] null: none
+    const float* hin;      // [T][D]
+    int gate_ld, D, gvec, gvec2;
+    float eps;
+};
+__global__ void postnorm_residual_kernel(PostArgs a) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
     pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     __shared__ float red[32];
-    const int t = blockIdx.x;
-    const float* mr = mo + (size_t)t * D;
-    float* xr = x + (size_t)t * D;
+    const int t = blockIdx.x, D = a.D;
+    float* mr = a.mo + (size_t)t * D;
+    float* xr = a.x + (size_t)t * D;
     float ss = 0.f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) ss += mr[d] * mr[d];
+    if (a.gate || a.idw) {
+        const float wi = a.idw ? a.idw[t] : 0.f;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            float v = mr[d];
+            if (a.idw) v = fmaf(wi, a.hin[(size_t)t * D + d], v);
+            if (a.gate) v *= 1.f / (1.f + expf(-(a.gate[(size_t)t * a.gate_ld + d] + a.gate_bias[d])));
+            mr[d] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) ss += mr[d] * mr[d];
+    }
     ss = block_sum(ss, red);
-    const float sc = gain[0] / sqrtf(ss / (float)D + eps);
+    const float sc = 1.f / sqrtf(ss / (float)D + a.eps);
     float s2 = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float v = xr[d] + mr[d] * sc;
+        const float v = xr[d] + mr[d] * sc * a.gain[a.gvec ? d : 0];
         xr[d] = v;
         s2 += v * v;
     }
-    if (gain2) {
+    if (a.gain2) {
         s2 = block_sum(s2, red);
-        const float sc2 = gain2[0] / sqrtf(s2 / (float)D + eps);
-        for (int d = threadIdx.x; d < D; d += blockDim.x) y[(size_t)t * D + d] = xr[d] * sc2;
+        const float sc2 = 1.f / sqrtf(s2 / (float)D + a.eps);
+        for (int d = threadIdx.x; d < D; d += blockDim.x) a.y[(size_t)t * D + d] = xr[d] * sc2 * a.gain2[a.gvec2 ? d : 0];
     }
 }
 
 // ---- matrix products: C[M, N] = epi(A[M, K] . W[N, K]^T) ----------------------------------------------------------------
-enum { EPI_NONE = 0, EPI_TANH = 1, EPI_SCALE = 2, EPI_SILU = 3 };
+enum { EPI_NONE = 0, EPI_TANH = 1, EPI_SCALE = 2, EPI_SILU = 3, EPI_SOFTCAP = 4 /* alpha * tanh(v / alpha) */, EPI_GELU_TANH = 5 };
 __device__ __forceinline__ float epi_apply(float v, int epi, float alpha) {
     if (epi == EPI_TANH) return tanhf(v);
     if (epi == EPI_SCALE) return v * alpha;
     if (epi == EPI_SILU) return v / (1.f + expf(-v));
+    if (epi == EPI_SOFTCAP) return alpha * tanhf(v / alpha);
+    if (epi == EPI_GELU_TANH) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
     return v;
 }
 
@@ -314,7 +345,7 @@ __device__ __forceinline__ void gemv_row_dot(const WT* w, const float* xs, int M
 // still running, and only then waits for that kernel's results (the rows).
 template <typename WT>
 __global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const float* A, int lda, const WT* W, float* C, int ldc, int M, int N, int K, int epi,
-                                                                  float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act) {
+                                                                  float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec) {
     extern __shared__ __align__(16) float xs[];   // [M][K]
     __shared__ float rss[kRowGemvMaxRows][kRowGemvThreads / 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -359,13 +390,12 @@ __global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const flo
     }
     __syncthreads();
     if (norm_gain) {
-        const float g = norm_gain[0];
         for (int r = 0; r < M; ++r) {
             float ss = 0.f;
             for (int w = 0; w < nw; ++w) ss += rss[r][w];
-            const float sc = g / sqrtf(ss / (float)K + eps);
+            const float sc = 1.f / sqrtf(ss / (float)K + eps);
             float* xr = xs + (size_t)r * K;
-            for (int k = threadIdx.x; k < K; k += blockDim.x) xr[k] = act_round<WT>(xr[k] * sc);
+            for (int k = threadIdx.x; k < K; k += blockDim.x) xr[k] = act_round<WT>(xr[k] * sc * norm_gain[gvec ? k : 0]);
         }
         __syncthreads();
     }
@@ -398,7 +428,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 template <bool GLU>
 __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int lda, const __nv_bfloat16* W, float* C, int ldc, int M, int N, int K, int epi,
-                                                           float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act) {
+                                                           float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int Kp = K + 32;
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smraw);                       // [M][Kp]
@@ -443,14 +473,19 @@ __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int 
         if (norm_gain) {
             float ss = 0.f;
             for (int w = 0; w < 8; ++w) ss += rss[r][w];
-            sc = norm_gain[0] / sqrtf(ss / (float)K + eps);
+            sc = (gvec ? 1.f : norm_gain[0]) / sqrtf(ss / (float)K + eps);
         }
+        const bool gv = norm_gain && gvec;
         const float* ar = A + (size_t)r * lda;
         __nv_bfloat16* xr = xs + (size_t)r * Kp;
         if (v4) {
 #pragma unroll 4
             for (int k = threadIdx.x * 4; k < K; k += 1024) {
-                const float4 v = *reinterpret_cast<const float4*>(ar + k);
+                float4 v = *reinterpret_cast<const float4*>(ar + k);
+                if (gv) {
+                    const float4 gn = *reinterpret_cast<const float4*>(norm_gain + k);
+                    v.x *= gn.x; v.y *= gn.y; v.z *= gn.z; v.w *= gn.w;
+                }
                 const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * sc, v.y * sc), hi = __floats2bfloat162_rn(v.z * sc, v.w * sc);
                 uint2 pk;
                 pk.x = *reinterpret_cast<const uint32_t*>(&lo);
@@ -458,7 +493,7 @@ __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int 
                 *reinterpret_cast<uint2*>(xr + k) = pk;
             }
         } else {
-            for (int k = threadIdx.x; k < K; k += blockDim.x) xr[k] = __float2bfloat16_rn(ar[k] * sc);
+            for (int k = threadIdx.x; k < K; k += blockDim.x) xr[k] = __float2bfloat16_rn(ar[k] * (gv ? norm_gain[k] : 1.f) * sc);
         }
     }
     __syncthreads();
@@ -594,7 +629,17 @@ struct AttnShape {
     int qk_norm, out_gate;
     float scale, eps;
     int ld;                           // row stride of the fused projection output [q | k | v | gate]
+    int v_ld;                         // token stride of the value pool; 0: kv_heads * vdim.  A cache whose values are the leading
+                                      // coordinates of its key rows passes the key pool as the value pool and the key stride here.
+    const float* sink;                // [heads] or null: the softmax denominator gains exp(sink[h]), a term without key or value
 };
+__device__ __forceinline__ size_t attn_vstride(const AttnShape& s) { return s.v_ld ? (size_t)s.v_ld : (size_t)s.kv_heads * s.vdim; }
+// the end of a softmax with a sink: (max, sum) -> the factor for the accumulated weighted values
+__device__ __forceinline__ float attn_finish_factor(const AttnShape& s, int h, float mx, float l) {
+    if (!s.sink) return 1.f / l;
+    const float sk = s.sink[h], m2 = fmaxf(mx, sk), c = expf(mx - m2);
+    return c / (l * c + expf(sk - m2));
+}
 // Rotation of q and k, unit RMS per head, and the cache append: one block per row.  q is rewritten in place; k and v go
 // to the row's page.  inv_freq[rot_dims / 2] holds the (scaled) frequencies; the angle is position * frequency in fp32.
 __global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const float* inv_freq, float* k_pool, float* v_pool) {
@@ -645,6 +690,8 @@ __global__ void attn_prepare_kernel(float* qkvg, StepMeta m, AttnShape s, const 
 // multiplied by sigmoid(gate) of its head.  out[t][h * dv ..].
 constexpr int kAttnWarps = 4;
 constexpr int kAttnMaxPerLane = 8;   // head sizes up to 256
+constexpr int kAttnWidePerLane = 20; // the wide instantiation: head sizes up to 640 (a low-rank cache row with its rotated part)
+template <int PL>
 __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const float* qkvg, StepMeta m, AttnShape s, const int* rows,
                                                                             const float* k_pool, const float* v_pool, float* out) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
@@ -657,22 +704,22 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const
     const int* table = m.page_table + (size_t)slot * m.table_stride;
     const int g = h / (s.heads / s.kv_heads);
     const float* q = qkvg + (size_t)t * s.ld + (size_t)h * s.dim;
-    float qr[kAttnMaxPerLane], o[kAttnMaxPerLane];
+    float qr[PL], o[PL];
 #pragma unroll
-    for (int i = 0; i < kAttnMaxPerLane; ++i) {
+    for (int i = 0; i < PL; ++i) {
         const int d = lane + 32 * i;
         qr[i] = d < s.dim ? q[d] : 0.f;
         o[i] = 0.f;
     }
     const int lo = (s.window > 0 && pos - s.window + 1 > 0) ? pos - s.window + 1 : 0;
     float mx = -INFINITY, l = 0.f;
-    const size_t kstride = (size_t)s.kv_heads * s.dim, vstride = (size_t)s.kv_heads * s.vdim;
+    const size_t kstride = (size_t)s.kv_heads * s.dim, vstride = attn_vstride(s);
     for (int j = lo + warp; j <= pos; j += kAttnWarps) {
         const size_t off = (size_t)table[j / kPageTokens] * kPageTokens + j % kPageTokens;
         const float* kr = k_pool + off * kstride + (size_t)g * s.dim;
         float sc = 0.f;
 #pragma unroll
-        for (int i = 0; i < kAttnMaxPerLane; ++i) {
+        for (int i = 0; i < PL; ++i) {
             const int d = lane + 32 * i;
             if (d < s.dim) sc = fmaf(qr[i], kr[d], sc);
         }
@@ -682,7 +729,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const
         l = l * corr + p;
         const float* vr = v_pool + off * vstride + (size_t)g * s.vdim;
 #pragma unroll
-        for (int i = 0; i < kAttnMaxPerLane; ++i) {
+        for (int i = 0; i < PL; ++i) {
             const int d = lane + 32 * i;
             if (d < s.vdim) o[i] = fmaf(p, vr[d], o[i] * corr);
         }
@@ -692,7 +739,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const
     float* pm = sm + kAttnWarps * s.vdim;
     float* pl = pm + kAttnWarps;
 #pragma unroll
-    for (int i = 0; i < kAttnMaxPerLane; ++i) {
+    for (int i = 0; i < PL; ++i) {
         const int d = lane + 32 * i;
         if (d < s.vdim) po[warp * s.vdim + d] = o[i];
     }
@@ -713,10 +760,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) window_attention_kernel(const
         const float z = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * s.dim + (size_t)s.kv_heads * s.vdim + h];
         gate = 1.f / (1.f + expf(-z));
     }
+    const float fin = attn_finish_factor(s, h, M, L) * gate;
     for (int d = threadIdx.x; d < s.vdim; d += blockDim.x) {
         float acc = 0.f;
         for (int w = 0; w < kAttnWarps; ++w) acc += po[w * s.vdim + d] * f[w];
-        out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc / L * gate;
+        out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc * fin;
     }
 }
 
@@ -752,7 +800,7 @@ __global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float
 #pragma unroll
         for (int j = 0; j < DV4 * 4; ++j) acc[i][j] = 0.f;
     }
-    const size_t kstride = (size_t)s.kv_heads * d, vstride = (size_t)s.kv_heads * dv;
+    const size_t kstride = (size_t)s.kv_heads * d, vstride = attn_vstride(s);
     for (int pg = lo / kPageTokens; pg <= hi / kPageTokens; ++pg) {
         __syncthreads();
         const size_t tok0 = (size_t)table[pg] * kPageTokens;
@@ -851,7 +899,7 @@ __global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float
             const float z = qkvg[(size_t)t * s.ld + (size_t)(s.heads + s.kv_heads) * d + (size_t)s.kv_heads * dv + h];
             gate = 1.f / (1.f + expf(-z));
         }
-        const float f = gate / lrow[i];
+        const float f = gate * attn_finish_factor(s, h, mrow[i], lrow[i]);
 #pragma unroll
         for (int jj = 0; jj < DV4; ++jj) {
             const int col = tx * 4 + 64 * jj;
@@ -1076,19 +1124,29 @@ __global__ void __launch_bounds__(32 * NW) wkv_scan_split_kernel(WkvArgs a, Step
 #pragma unroll
     for (int i = 0; i < RP; ++i) Sg[(size_t)(warp * RP + i) * D + j] = S[i];
 }
-// o[t, head] / rms(o[t, head]) * normw * gate, in place: one warp per (row, head)
-__global__ void wkv_finish_kernel(float* o, const float* gate, const float* normw, int T, int heads, int d, float eps) {
+// o[t, head] / rms(o[t, head]) * normw * gate, in place: one warp per (row, head).  d = the head's output size; normw is
+// [heads][d] (w_heads = 1) or one [d] vector shared by the heads (w_heads = 0); gate (optional) has row stride gate_ld and is
+// used as it is (gate_silu = 0) or through z * sigmoid(z) (gate_silu = 1).
+__global__ void head_rmsnorm_gate_kernel(float* o, const float* gate, int gate_ld, int gate_silu, const float* normw, int w_heads, int T, int heads, int d,
+                                         float eps) {
     pdl_launch_dependents();   // the kernel behind this one may be scheduled (and a few-row product may fetch its weights) ...
     pdl_wait_prior_grid();     // ... while this one waits here for the kernel before it, when it was launched ahead of its end
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= T * heads) return;
-    const int hd = warp % heads;
-    const size_t base = (size_t)(warp / heads) * heads * d + (size_t)hd * d;
+    const int hd = warp % heads, t = warp / heads;
+    const size_t base = (size_t)t * heads * d + (size_t)hd * d;
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) ss += o[base + i] * o[base + i];
     ss = warp_sum(ss);
     const float sc = 1.f / sqrtf(ss / (float)d + eps);
-    for (int i = lane; i < d; i += 32) o[base + i] = o[base + i] * sc * normw[hd * d + i] * gate[base + i];
+    for (int i = lane; i < d; i += 32) {
+        float g = 1.f;
+        if (gate) {
+            g = gate[(size_t)t * gate_ld + (size_t)hd * d + i];
+            if (gate_silu) g = g / (1.f + expf(-g));
+        }
+        o[base + i] = o[base + i] * sc * normw[(w_heads ? hd * d : 0) + i] * g;
+    }
 }
 
 // ---- helpers -----------------------------------------------------------------------------------------------------------

@@ -6,6 +6,10 @@ reads folder/config.json and folder/model.safetensors.  Registered architectures
   * "Binusun"  -- layer list of windowed rotary attention / token-shifted linear recurrence (wkv) mixers with scalar-gain RMS
                   norms around every sublayer, an optional looped block of layers; runs on the layered sequence engine
                   (turboinfer_b200.seq, include/ti_b200_seq.h).
+  * "Tudasun"  -- layer list of gated-linear-attention / HGRN2 recurrences and latent attention (low-rank key/value cache, rotated
+                  key part shared by the heads, softmax sink, optional reuse of an earlier layer's cache), dense feed-forward with a
+                  polynomial-norm activation or routed experts (group-limited choice, identity experts, shared expert), gated
+                  residuals, a per-layer token side input and capped logits; runs on the layered sequence engine too.
   * "llama"    -- the quantized Llama-style decoder of the persistent decode kernel (turboinfer_b200.capi.Model); built from
                   {"hidden", "layers", "heads", "inter", "vocab"} and fp32 tensors under the reference's names.
 """
@@ -87,6 +91,78 @@ def _load_binusun(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seq
     mode = {"bfloat16": _seq.BF16, "float32": _seq.F32}[dtype]
     shapes = {k: tuple(getattr(v, "shape", ())) for k, v in weights.items()}
     desc, layers = binusun_descs(cfg, mode, max_tokens, max_seqs, shapes)
+    return _seq.SeqModel(desc, layers).load(weights)
+
+
+def tudasun_descs(cfg: dict, mode: int, max_tokens: int, max_seqs: int, tensor_shapes: Dict[str, Tuple[int, ...]] = None):
+    """config.json of a Tudasun model -> (ModelDesc, [LayerDesc]).  The inner size of the gla decay projection, which the
+    configuration does not carry, is the row count of the checkpoint's l<i>.mix.a1; the gated residual is on when the
+    checkpoint has l<i>.rg1."""
+    shapes = tensor_shapes or {}
+    layers: List[_seq.LayerDesc] = []
+    for i, L in enumerate(_req(cfg, "layers", "the model")):
+        where = f"layer {i}"
+        mx = _req(L, "mixer", where)
+        d = _seq.LayerDesc()
+        kind = _req(L, "type", where)
+        d.heads, d.dim, d.vdim = int(_req(mx, "heads", where)), int(_req(mx, "dim", where)), int(_req(mx, "vdim", where))
+        d.kv_heads = d.heads
+        if kind == "gla":
+            d.mixer = _seq.MIXER_GLA
+            d.decay_tau = float(_req(mx, "tau", where))
+            shape = shapes.get(f"l{i}.mix.a1")
+            if not shape:
+                raise ValueError(f"{where}: the decay projection l{i}.mix.a1 is missing from the checkpoint")
+            d.decay_rank = int(shape[0])
+        elif kind == "hgrn2":
+            d.mixer = _seq.MIXER_HGRN2
+        elif kind == "latent_attention":
+            d.mixer = _seq.MIXER_LATENT
+            d.kv_rank, d.rot_dims = int(_req(mx, "kv_rank", where)), int(_req(mx, "rot_dim", where))
+            rot = _req(mx, "rot", where)
+            if int(_req(rot, "dims", where + " rot")) != d.rot_dims:
+                raise ValueError(f"{where}: rot.dims {rot['dims']} differs from rot_dim {d.rot_dims}; the rotated part turns as a whole")
+            d.rot_base = float(_req(rot, "base", where + " rot"))
+            d.scale = float(_req(mx, "scale", where))
+            d.kv_from = int(mx["kv_from"]) if mx.get("kv_from") is not None else -1
+            d.sink = 1
+        else:
+            raise ValueError(f"{where}: unknown mixer type '{kind}'")
+        d.res_gate = 1 if (not shapes or f"l{i}.rg1" in shapes) else 0
+        mlp = L.get("mlp")
+        if mlp:
+            fk = _req(mlp, "kind", where + " mlp")
+            if fk == "dense":
+                d.ff_kind, d.ff = _seq.FF_POLYNORM, int(_req(mlp, "ff", where + " mlp"))
+            elif fk == "moe":
+                r = _req(mlp, "router", where + " mlp")
+                d.ff_kind, d.ff = _seq.FF_EXPERTS, int(_req(_req(mlp, "expert", where + " mlp"), "ff", where + " mlp.expert"))
+                d.experts, d.top = int(_req(r, "experts", where + " router")), int(_req(r, "top", where + " router"))
+                d.identity = int(r.get("identity") or 0)
+                g = r.get("groups") or {}
+                d.groups, d.groups_keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
+                sh = mlp.get("shared")
+                d.shared_ff = int(_req(sh, "ff", where + " mlp.shared")) if sh else 0
+            else:
+                raise ValueError(f"{where}: unknown feed-forward kind '{fk}'")
+        layers.append(d)
+    m = _seq.ModelDesc()
+    m.vocab, m.width, m.n_layers = int(_req(cfg, "vocab", "the model")), int(_req(cfg, "width", "the model")), len(layers)
+    m.norm_eps = float(_req(_req(cfg, "norm", "the model"), "eps", "norm"))
+    m.norm_kind = _seq.NORM_ONE_PLUS
+    m.logit_scale = 1.0
+    m.logit_softcap = float(cfg.get("logit_softcap") or 0.0)
+    ts = cfg.get("token_side")
+    m.side_dim = int(_req(ts, "dim", "token_side")) if ts else 0
+    m.mode, m.max_tokens, m.max_seqs = mode, int(max_tokens), int(max_seqs)
+    return m, layers
+
+
+@register("Tudasun")
+def _load_tudasun(cfg: dict, weights: dict, dtype: str, max_tokens: int, max_seqs: int):
+    mode = {"bfloat16": _seq.BF16, "float32": _seq.F32}[dtype]
+    shapes = {k: tuple(getattr(v, "shape", ())) for k, v in weights.items()}
+    desc, layers = tudasun_descs(cfg, mode, max_tokens, max_seqs, shapes)
     return _seq.SeqModel(desc, layers).load(weights)
 
 
