@@ -1027,7 +1027,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 float* wdense = m.route.p;
                 float* idw_buf = m.route.p + (size_t)T * std::max(Ex, 1);
                 const int rw = 4;
-                const size_t rsm = (size_t)rw * (2 * (Ex + L.d.identity) + L.d.groups) * sizeof(float);
+                const size_t rsm = (size_t)rw * (2 * (Ex + L.d.identity) + 2 * L.d.groups) * sizeof(float);
                 TRY(launch_dep(moe_route_kernel, dim3((T + rw - 1) / rw), dim3(rw * 32), rsm, (const float*)m.proj.p, nfw, L.off_router, r, L.correction, T, wdense, idw_buf));
                 LAUNCHED();
                 if (L.ff_width > 0) {

@@ -44,17 +44,18 @@ struct RouteShape {
 // One warp per row.  s = softmax(logits); choice = s + correction; the best `keep` groups by their largest choice score stay, the
 // `top` largest choice scores among them are picked (first index wins a tie); weights = s over the picked ones / (their sum + 1e-20).
 // wdense[t][e] = weight of real expert e or 0; idw[t] = sum of the weights of picked identity experts.
-// Shared memory per warp: s[n], choice[n], group score[groups].
+// Shared memory per warp: s[n], choice[n], group score[groups], group kept[groups].
 __global__ void moe_route_kernel(const float* proj, int ld, int off, RouteShape r, const float* correction, int T, float* wdense, float* idw) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     extern __shared__ float rsm[];
-    const int n = r.n_real + r.n_id, per = 2 * n + r.groups;
+    const int n = r.n_real + r.n_id, per = 2 * n + 2 * r.groups;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= T) return;
     float* s = rsm + (size_t)warp * per;
     float* ch = s + n;
     float* gs = ch + n;
+    float* kept = gs + r.groups;
     const float* z = proj + (size_t)t * ld + off;
     float mx = -INFINITY;
     for (int i = lane; i < n; i += 32) mx = fmaxf(mx, z[i]);
@@ -76,6 +77,7 @@ __global__ void moe_route_kernel(const float* proj, int ld, int off, RouteShape 
         float b = -INFINITY;
         for (int i = g * size; i < (g + 1) * size; ++i) b = fmaxf(b, ch[i]);
         gs[g] = b;
+        kept[g] = 0.f;
     }
     __syncwarp();
     // keep the best groups: a group outside them has its members' choice scores set to -inf
@@ -90,11 +92,14 @@ __global__ void moe_route_kernel(const float* proj, int ld, int off, RouteShape 
                 const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
                 if (ob > b || (ob == b && oi < bi)) { b = ob; bi = oi; }
             }
-            if (lane == 0 && bi != 0x7FFFFFFF) gs[bi] = INFINITY;   // marked as kept
+            if (lane == 0 && bi != 0x7FFFFFFF) {
+                kept[bi] = 1.f;
+                gs[bi] = -INFINITY;   // not to be found again
+            }
             __syncwarp();
         }
         for (int i = lane; i < n; i += 32)
-            if (gs[i / size] != INFINITY) ch[i] = -INFINITY;
+            if (kept[i / size] == 0.f) ch[i] = -INFINITY;
         __syncwarp();
     }
     for (int i = lane; i < r.n_real; i += 32) wdense[(size_t)t * r.n_real + i] = 0.f;
