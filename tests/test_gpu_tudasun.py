@@ -45,6 +45,7 @@ MECHANISMS = {
     "gla": make_config([gla_layer()]),
     "gla_wide_keys_one_head": make_config([gla_layer(heads=1, dim=40, vdim=24, tau=3.0, rank=5), gla_layer(heads=2, dim=72, vdim=33, rank=1)], width=40, side=0),
     "gla_state_in_shared_memory": make_config([gla_layer(heads=1, dim=136, vdim=40, rank=3)], width=64),
+    "recurrence_128_key_channels": make_config([hgrn2_layer(heads=1, dim=128, vdim=40), gla_layer(heads=2, dim=128, vdim=96, rank=2)], width=64),
     "hgrn2": make_config([hgrn2_layer()]),
     "hgrn2_equal_sizes": make_config([hgrn2_layer(heads=2, dim=32, vdim=32), hgrn2_layer(heads=1, dim=64, vdim=8)], softcap=0),
     "latent": make_config([latent_layer()]),

@@ -34,14 +34,46 @@ def config_for(size: str) -> dict:
             "logit_scale": 1.0, "vocab": z["vocab"], "width": z["width"]}
 
 
+def tudasun_config_for(size: str) -> dict:
+    """Seven layers in the order gla, latent attention, gla, hgrn2, latent attention on the second layer's cache, gla, hgrn2; dense
+    feed-forwards at both ends, routed experts (8 of a quarter of the dense inner size, 2 identity experts, 2 chosen from the best of
+    2 groups, a shared expert of half the dense size) in between.  The low-rank cache row is 256 + 64 wide."""
+    z = SIZES[size]
+    D, ff = z["width"], z["ff"]
+    H = z["heads"]
+    gla = {"type": "gla", "mixer": {"heads": H, "dim": 64, "vdim": 128, "tau": 16.0}}
+    hg = {"type": "hgrn2", "mixer": {"heads": H, "dim": 128, "vdim": 128}}
+    lat = {"type": "latent_attention", "mixer": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 256, "rot": {"base": 10000.0, "dims": 64},
+                                                 "scale": 1.0 / math.sqrt(192.0)}}
+    lat2 = {"type": "latent_attention", "mixer": dict(lat["mixer"], kv_from=1)}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 8, "identity": 2, "top": 2, "groups": {"count": 2, "keep": 1}}, "shared": {"ff": ff // 2}}
+    order = [(gla, dense), (lat, moe), (gla, moe), (hg, moe), (lat2, moe), (gla, dense), (hg, dense)]
+    return {"architecture": "Tudasun", "layers": [dict(a, mlp=b) for a, b in order], "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "token_side": {"dim": 64}, "vocab": z["vocab"], "width": D}
+
+
 def build_synthetic(cfg: dict, rank: int, dtype: str, max_tokens: int, max_seqs: int) -> seq.SeqModel:
     mode = {"bfloat16": seq.BF16, "float32": seq.F32}[dtype]
-    shapes = {f"l{i}.mix.w1": (rank, cfg["width"]) for i, L in enumerate(cfg["layers"]) if L["type"] == "wkv"}
-    desc, layers = models.binusun_descs(cfg, mode, max_tokens, max_seqs, shapes)
+    if cfg["architecture"] == "Tudasun":
+        shapes = {f"l{i}.mix.a1": (rank, cfg["width"]) for i, L in enumerate(cfg["layers"]) if L["type"] == "gla"}
+        shapes.update({f"l{i}.rg1": (cfg["width"], cfg["width"]) for i in range(len(cfg["layers"]))})
+        desc, layers = models.tudasun_descs(cfg, mode, max_tokens, max_seqs, shapes)
+    else:
+        shapes = {f"l{i}.mix.w1": (rank, cfg["width"]) for i, L in enumerate(cfg["layers"]) if L["type"] == "wkv"}
+        desc, layers = models.binusun_descs(cfg, mode, max_tokens, max_seqs, shapes)
     m = seq.SeqModel(desc, layers)
     for k, (name, shape) in enumerate(m.tensor_specs()):
         leaf = name.split(".")[-1]
-        if len(shape) == 0:
+        if cfg["architecture"] == "Tudasun" and (leaf in ("norm1", "norm1b", "norm2", "norm2b", "b", "correction") or name == "final.norm"):
+            amp, off = 0.1, (1.0 if name.endswith("a2.b") else 0.0)   # gains stored around zero, biases, router corrections
+        elif leaf == "lower":
+            amp, off = 0.45, 0.45
+        elif leaf in ("sink", "act"):
+            amp, off = 1.0, 0.0
+        elif name == "side.embed":
+            amp, off = 1.0, 0.0
+        elif len(shape) == 0:
             amp, off = 0.25, 1.0
         elif ".mu." in name:
             amp, off = 0.5, 0.5
@@ -63,8 +95,8 @@ def prompt(n: int, vocab: int, offset: int = 0):
     return [int((7919 * i + 1 + offset) % vocab) for i in range(n)]
 
 
-def measure_seq(size: str, dtype: str, n_prompt: int, n_new: int, batch: int, steps: int, warmup: int) -> dict:
-    cfg = config_for(size)
+def measure_seq(size: str, dtype: str, n_prompt: int, n_new: int, batch: int, steps: int, warmup: int, design: str = "Binusun") -> dict:
+    cfg = tudasun_config_for(size) if design == "Tudasun" else config_for(size)
     m = build_synthetic(cfg, SIZES[size]["rank"], dtype, max_tokens=(n_prompt + n_new + 64) * max(batch, 1) + 64, max_seqs=max(batch, 1))
     V = cfg["vocab"]
     launches0 = seq.launch_count()
@@ -123,6 +155,16 @@ def measure_llama(size: str, n_prompt: int, n_new: int, steps: int, warmup: int)
     return {"prefill_tokens_per_s": n_prompt / (pre_ms * 1e-3), "prefill_ms": pre_ms, "decode_tokens_per_s": 1.0 / (dec_ms * 1e-3),
             "decode_ms_per_step": dec_ms, "weight_bytes": wb, "decode_weight_GBps": wb / (dec_ms * 1e-3) / 1e9,
             "e2e_s_per_generation": statistics.median(wall), "weights": "int4", "layers": 7}
+
+
+def compare_tudasun(size: str, steps: int, warmup: int, n_prompt: int = 2048, n_new: int = 64) -> dict:
+    """Tudasun next to the closest model of the library, the Binusun hybrid on the same engine (bf16 weights, 7 layer runs each)."""
+    out = {"size": size, "shape": SIZES[size], "prompt_tokens": n_prompt, "decode_steps": n_new}
+    for design in ("Tudasun", "Binusun"):
+        key = design.lower() + "_bf16"
+        out[key] = measure_seq(size, "bfloat16", n_prompt, n_new, 1, steps, warmup, design)
+        out[key + "_batch4"] = {k: v for k, v in measure_seq(size, "bfloat16", 256, n_new, 4, 1, 1, design).items() if k.startswith("decode") or k == "batch"}
+    return out
 
 
 def compare(size: str, steps: int, warmup: int, n_prompt: int = 2048, n_new: int = 64, with_llama: bool = True) -> dict:

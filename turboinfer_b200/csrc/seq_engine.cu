@@ -608,6 +608,23 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
     return 0;
 }
 
+// one small product per head: C[r][h * c_stride + n] = sum_k A[r][h * a_stride + k] W[h][n][k]; few rows in one launch, else a product per head
+int gemm_heads(Model& m, const float* A, int lda, int a_stride, const void* W, float* C, int ldc, int c_stride, int heads, int M, int N, int K) {
+    if (M <= kRowGemvMaxRows && (size_t)M * K * sizeof(float) <= 48 * 1024) {
+        const int warps = kRowGemvThreads / 32;
+        const dim3 grid(std::max(1, std::min((N + warps - 1) / warps, std::max(1, 4 * g_num_sms / heads))), heads);
+        if (m.d.mode == TI_SEQ_BF16)
+            TRY(launch_dep(gemv_heads_rows_kernel<__nv_bfloat16>, grid, dim3(kRowGemvThreads), (size_t)M * K * sizeof(float), A, lda, a_stride, (const __nv_bfloat16*)W, C, ldc, c_stride, M, N, K));
+        else
+            TRY(launch_dep(gemv_heads_rows_kernel<float>, grid, dim3(kRowGemvThreads), (size_t)M * K * sizeof(float), A, lda, a_stride, (const float*)W, C, ldc, c_stride, M, N, K));
+        LAUNCHED();
+        return 0;
+    }
+    for (int h = 0; h < heads; ++h)
+        TRY(gemm(m, A + (size_t)h * a_stride, lda, (const uint8_t*)W + (size_t)h * N * K * m.wsize, C + (size_t)h * c_stride, ldc, M, N, K));
+    return 0;
+}
+
 int ensure_scratch(Model& m, int rows, int want) {
     if (rows > m.cap_rows) {
         const size_t R = (size_t)std::max(rows, 64), D = m.d.width;
@@ -800,7 +817,6 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     LAUNCHED();
     const float eps = m.d.norm_eps;
     const int gv = m.gvec;
-    const size_t ws = m.wsize;
     // the end of a sublayer: (identity experts) -> (gate) -> norm behind the sublayer -> residual sum (-> the next sublayer's input)
     auto post = [&](const float* gain, int gain_vec, const float* gain2, const float* gate, int gate_ld, const float* gate_bias, const float* idw) -> int {
         PostArgs a{};
@@ -814,7 +830,8 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
     auto attention = [&](const AttnShape& s, const float* q, const float* kp, const float* vp, float* out) -> int {
         const bool wide = std::max(s.dim, s.vdim) > 32 * kAttnMaxPerLane;
         const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
-        const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim);
+        const bool v_in_k = kp == vp && s.kv_heads == 1 && s.v_ld == s.dim && s.vdim <= s.dim;
+        const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim, v_in_k);
         const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && tsmem <= g_smem_optin && (s.v_ld % 4 == 0);
         // bf16 mode, head sizes 64 / 128: the split-half tensor-core kernel (fp32-accurate); fp32 mode keeps true fp32 arithmetic
         const bool h3_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles128 > 0 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
@@ -956,7 +973,11 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             a.state = R.state.p; a.out = m.att.p; a.heads = H; a.dk = dk; a.dv = dv;
             const int threads = std::min(128, (dv + 31) / 32 * 32);
             const dim3 grid(E, H, (dv + threads - 1) / threads);
-            if (dk <= 32) TRY(launch_dep(linear_scan_kernel<32>, grid, dim3(threads), linear_scan_smem_bytes(dk, threads, false), a, sm));
+            const int zg = (dv + 31) / 32;
+            if (dk == 32) TRY(launch_dep(linear_scan_split_kernel<32, 8, 4>, dim3(E, H, zg), dim3(128), 0, a, sm));
+            else if (dk == 64) TRY(launch_dep(linear_scan_split_kernel<64, 8, 8>, dim3(E, H, zg), dim3(256), 0, a, sm));
+            else if (dk == 128) TRY(launch_dep(linear_scan_split_kernel<128, 4, 16>, dim3(E, H, zg), dim3(512), 0, a, sm));
+            else if (dk <= 32) TRY(launch_dep(linear_scan_kernel<32>, grid, dim3(threads), linear_scan_smem_bytes(dk, threads, false), a, sm));
             else if (dk <= 64) TRY(launch_dep(linear_scan_kernel<64>, grid, dim3(threads), linear_scan_smem_bytes(dk, threads, false), a, sm));
             else if (dk <= 128) TRY(launch_dep(linear_scan_kernel<128>, grid, dim3(threads), linear_scan_smem_bytes(dk, threads, false), a, sm));
             else {
@@ -979,15 +1000,13 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             TRY(launch_dep(latent_prepare_kernel, dim3(T), dim3(128), 0, (const float*)m.proj.p, sm, ls, (const float*)L.inv_freq.p, L.cnorm, pool, m.aux.p));
             LAUNCHED();
             // the key up-projection moves to the query: qabs[t][h][0 .. rank) = Uk_h^T q_h
-            for (int h = 0; h < H; ++h)
-                TRY(gemm(m, m.proj.p + L.off_q + (size_t)h * (d + dr), nf, L.ukT.p + (size_t)h * rank * d * ws, m.aux.p + (size_t)h * kd, H * kd, T, rank, d));
+            TRY(gemm_heads(m, m.proj.p + L.off_q, nf, d + dr, L.ukT.p, m.aux.p, H * kd, kd, H, T, rank, d));
             AttnShape s{};
             s.heads = H; s.kv_heads = 1; s.dim = kd; s.vdim = rank; s.window = 0; s.rot_dims = 0; s.qk_norm = 0; s.out_gate = 0;
             s.scale = L.d.scale; s.eps = eps; s.ld = H * kd; s.v_ld = kd; s.sink = L.sink;
             TRY(attention(s, m.aux.p, pool, pool, m.aux2.p));
             // ... and the value up-projection behind the weighted sum: att[t][h] = Uv_h (sum_j p_j c_j)
-            for (int h = 0; h < H; ++h)
-                TRY(gemm(m, m.aux2.p + (size_t)h * rank, H * rank, (const uint8_t*)L.uv + (size_t)h * dv * rank * ws, m.att.p + (size_t)h * dv, H * dv, T, dv, rank));
+            TRY(gemm_heads(m, m.aux2.p, H * rank, rank, L.uv, m.att.p, H * dv, dv, H, T, dv, rank));
             TRY(gemm(m, m.att.p, H * dv, L.o, m.mo.p, D, T, D, H * dv));
         }
         if (L.d.ff > 0) {

@@ -412,6 +412,30 @@ __global__ void __launch_bounds__(kRowGemvThreads, 2) gemv_rows_kernel(const flo
     }
 }
 
+// Few rows, one small matrix per head: C[r][h * c_stride + n] = sum_k A[r][h * a_stride + k] * W[h][n][k] (W: [heads][N][K]).
+// grid (column groups, heads); the head's slice of the rows sits in shared memory, one warp per output column.
+template <typename WT>
+__global__ void __launch_bounds__(kRowGemvThreads) gemv_heads_rows_kernel(const float* A, int lda, int a_stride, const WT* W, float* C, int ldc, int c_stride, int M, int N,
+                                                                           int K) {
+    extern __shared__ __align__(16) float xs[];   // [M][K]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, h = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = act_round<WT>(A[(size_t)(i / K) * lda + (size_t)h * a_stride + i % K]);
+    __syncthreads();
+    const WT* Wh = W + (size_t)h * N * K;
+    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(Wh) & 15) == 0);
+    float acc[kRowGemvMaxRows];
+    for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
+        gemv_row_dot<WT>(Wh + (size_t)n * K, xs, M, K, vec, lane, acc);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < kRowGemvMaxRows; ++r)
+                if (r < M) C[(size_t)r * ldc + (size_t)h * c_stride + n] = acc[r];
+        }
+    }
+}
+
 // The same few-row product on the warp-level tensor cores (bf16 weights, bf16-rounded rows, fp32 accumulators): the cost of a
 // weight byte no longer grows with the number of rows.  A block owns 16 output columns, its 8 warps split K; a lane (g = lane / 4,
 // t = lane % 4) reads 16 bytes of column g and of column g + 8 straight from global memory and 16 bytes of row g from shared
@@ -778,10 +802,13 @@ __global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float
                                                                       const float* k_pool, const float* v_pool, float* out) {
     extern __shared__ __align__(16) float smt[];
     const int d = s.dim, dv = s.vdim, ldq = d + 4, ldp = kAttnTile + 4;
+    // a cache whose values are the leading coordinates of its key rows (one key/value head): the value tile IS the key tile
+    const bool v_in_k = (v_pool == k_pool) && s.kv_heads == 1 && s.v_ld == s.dim && dv <= d;
+    const int ldvs = v_in_k ? ldq : dv;
     float* Qs = smt;
     float* Ks = Qs + kAttnTile * ldq;
-    float* Vs = Ks + kAttnTile * ldq;
-    float* Ps = Vs + kAttnTile * dv;
+    float* Vs = v_in_k ? Ks : Ks + kAttnTile * ldq;
+    float* Ps = Vs + (v_in_k ? kAttnTile * ldq : kAttnTile * dv);
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int row0 = tiles[2 * blockIdx.x], n = tiles[2 * blockIdx.x + 1], h = blockIdx.y;
     const int p0 = m.row_pos[row0];
@@ -811,7 +838,7 @@ __global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float
             const float4 v = (key >= lo && key <= hi) ? *reinterpret_cast<const float4*>(kb + (size_t)c * kstride + k4) : make_float4(0.f, 0.f, 0.f, 0.f);
             *reinterpret_cast<float4*>(&Ks[c * ldq + k4]) = v;
         }
-        for (int i = tid; i < kAttnTile * (dv / 4); i += 256) {
+        for (int i = tid; i < (v_in_k ? 0 : kAttnTile * (dv / 4)); i += 256) {
             const int c = i / (dv / 4), k4 = (i % (dv / 4)) * 4, key = pg * kPageTokens + c;
             const float4 v = (key >= lo && key <= hi) ? *reinterpret_cast<const float4*>(vb + (size_t)c * vstride + k4) : make_float4(0.f, 0.f, 0.f, 0.f);
             *reinterpret_cast<float4*>(&Vs[c * dv + k4]) = v;
@@ -875,7 +902,7 @@ __global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float
                 for (int jj = 0; jj < DV4; ++jj) {
                     const int col = tx * 4 + 64 * jj;
                     if (col < dv) {
-                        const float4 v = *reinterpret_cast<const float4*>(&Vs[(c + cc) * dv + col]);
+                        const float4 v = *reinterpret_cast<const float4*>(&Vs[(c + cc) * ldvs + col]);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const float p = cc == 0 ? pr[i].x : cc == 1 ? pr[i].y : cc == 2 ? pr[i].z : pr[i].w;
@@ -913,7 +940,9 @@ __global__ void __launch_bounds__(256) window_attention_tiled_kernel(const float
         }
     }
 }
-inline size_t attn_tiled_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t)2 * kAttnTile * (d + 4) + (size_t)kAttnTile * dv + (size_t)kAttnTile * (kAttnTile + 4)); }
+inline size_t attn_tiled_smem_bytes(int d, int dv, bool v_in_k = false) {
+    return sizeof(float) * ((size_t)2 * kAttnTile * (d + 4) + (v_in_k ? 0 : (size_t)kAttnTile * dv) + (size_t)kAttnTile * (kAttnTile + 4));
+}
 
 // ---- gated feed-forward: act(gate) * up over the fused projection output [gate | up] ------------------------------------
 enum { ACT_RELU = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };

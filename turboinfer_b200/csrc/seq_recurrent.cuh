@@ -130,6 +130,106 @@ __global__ void __launch_bounds__(128) linear_scan_kernel(LinScanArgs a, StepMet
         }
     }
 }
+// Key channels of 32 / 64 / 128: a BLOCK owns 32 value columns of a head (grid z = column group) and its NW warps split the key
+// channels, so a lane keeps DK / NW entries of its state column in registers and a token costs DK / NW dependent multiply-adds a
+// lane instead of DK.  Tokens are taken CH at a time: the chunk's q, w, a vectors and v columns go to shared memory while the
+// NEXT chunk's operands are already requested; every warp runs the chunk's tokens over its channels and leaves a partial
+// output per token; the NW partials are summed in warp order (the result does not depend on timing).  The organisation of the
+// wkv scan of seq_kernels.cuh, with the output read after the update and value columns that need not be as many as key channels.
+template <int DK, int CH, int NW>
+__global__ void __launch_bounds__(32 * NW) linear_scan_split_kernel(LinScanArgs a, StepMeta m) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    constexpr int RP = DK / NW, NT = 32 * NW, PER = CH * DK / NT, VPER = (CH * 32 + NT - 1) / NT;
+    static_assert(DK % NW == 0 && RP % 4 == 0 && (CH * DK) % NT == 0, "chunk staging must divide evenly");
+    __shared__ __align__(16) float buf[CH][3][DK];
+    __shared__ float vbuf[CH][32];
+    __shared__ float part[NW][CH][32];
+    const int e = blockIdx.x, hd = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int dv = a.dv, col0 = blockIdx.z * 32, j = col0 + lane;
+    const bool own = j < dv;
+    float* Sg = a.state + ((size_t)m.ent_slot[e] * a.heads + hd) * (size_t)DK * dv;
+    const bool fresh = (m.ent_pos0[e] == 0);
+    float S[RP];
+#pragma unroll
+    for (int i = 0; i < RP; ++i) S[i] = (own && !fresh) ? Sg[(size_t)(warp * RP + i) * dv + j] : 0.f;
+    const int t0 = m.ent_row0[e], t1 = m.ent_row0[e + 1];
+    float nq[PER], nk[PER], na[PER], nv[VPER];
+    auto fetch = [&](int tc) {
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+            const int x = tid + NT * p, c = x / DK, i = x % DK;
+            const size_t t = (size_t)min(tc + c, t1 - 1);
+            nq[p] = a.q[t * a.ldq + (size_t)hd * DK + i];
+            na[p] = a.a[t * a.lda + (size_t)hd * DK + i];
+            nk[p] = a.k ? a.k[t * a.ldk + (size_t)hd * DK + i] : 0.f;
+        }
+#pragma unroll
+        for (int p = 0; p < VPER; ++p) {
+            const int x = tid + NT * p, c = x >> 5, l = x & 31;
+            nv[p] = (c < CH && col0 + l < dv) ? a.v[(size_t)min(tc + c, t1 - 1) * a.ldv + (size_t)hd * dv + col0 + l] : 0.f;
+        }
+    };
+    auto emit = [&](int tc) {   // out[t][j] = sum over the warps' partials, chunk starting at row tc
+        for (int x = tid; x < CH * 32; x += NT) {
+            const int c = x >> 5, l = x & 31;
+            if (tc + c < t1 && col0 + l < dv) {
+                float s = part[0][c][l];
+#pragma unroll
+                for (int w = 1; w < NW; ++w) s += part[w][c][l];
+                a.out[(size_t)(tc + c) * (a.heads * dv) + (size_t)hd * dv + col0 + l] = s;
+            }
+        }
+    };
+    fetch(t0);
+    for (int tc = t0; tc < t1; tc += CH) {
+        if (tc > t0) emit(tc - CH);
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+            const int x = tid + NT * p, c = x / DK, i = x % DK;
+            buf[c][0][i] = nq[p] * a.qscale;
+            buf[c][1][i] = a.k ? nk[p] : 1.f - na[p];
+            buf[c][2][i] = na[p];
+        }
+#pragma unroll
+        for (int p = 0; p < VPER; ++p) {
+            const int x = tid + NT * p;
+            if (x < CH * 32) vbuf[x >> 5][x & 31] = nv[p];
+        }
+        __syncthreads();
+        if (tc + CH < t1) fetch(tc + CH);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            if (tc + c < t1) {
+                float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+                const float v = vbuf[c][lane];
+#pragma unroll
+                for (int i = 0; i < RP; i += 4) {
+                    const int ch = warp * RP + i;
+                    const float4 q4 = *reinterpret_cast<const float4*>(&buf[c][0][ch]);
+                    const float4 w4 = *reinterpret_cast<const float4*>(&buf[c][1][ch]);
+                    const float4 a4 = *reinterpret_cast<const float4*>(&buf[c][2][ch]);
+                    S[i] = fmaf(a4.x, S[i], w4.x * v);
+                    acc0 = fmaf(q4.x, S[i], acc0);
+                    S[i + 1] = fmaf(a4.y, S[i + 1], w4.y * v);
+                    acc1 = fmaf(q4.y, S[i + 1], acc1);
+                    S[i + 2] = fmaf(a4.z, S[i + 2], w4.z * v);
+                    acc2 = fmaf(q4.z, S[i + 2], acc2);
+                    S[i + 3] = fmaf(a4.w, S[i + 3], w4.w * v);
+                    acc3 = fmaf(q4.w, S[i + 3], acc3);
+                }
+                part[warp][c][lane] = (acc0 + acc1) + (acc2 + acc3);
+            }
+        }
+        __syncthreads();
+    }
+    emit(t0 + (t1 - t0 - 1) / CH * CH);
+    if (own) {
+#pragma unroll
+        for (int i = 0; i < RP; ++i) Sg[(size_t)(warp * RP + i) * dv + j] = S[i];
+    }
+}
+
 inline size_t linear_scan_smem_bytes(int dk, int threads, bool state_in_smem) {
     return sizeof(float) * ((size_t)kLinScanChunk * (3 * dk + threads) + (state_in_smem ? (size_t)dk * threads : 0));
 }
