@@ -59,7 +59,7 @@ MECHANISMS = {
     "experts_many": make_config([gla_layer(mlp=moe(experts=37, identity=3, top=6, count=8, keep=3, ff=8, shared=0))]),
     "no_side_input_no_cap": make_config([gla_layer(mlp=dense(32)), latent_layer()], side=0, softcap=0),
     "hybrid": make_config([gla_layer(mlp=dense(40)), latent_layer(mlp=moe()), hgrn2_layer(mlp=moe(experts=2, identity=1, top=2, count=3, keep=2)),
-                           latent_layer(heads=3, kv_from=1), hgrn2_layer()], vocab=101, width=56, side=3),
+                           latent_layer(heads=3, kv_from=1), hgrn2_layer()], vocab=101, width=56, side=7),
 }
 
 

@@ -536,16 +536,25 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
          const Fuse* fuse = nullptr) {
     if (M <= 0 || N <= 0) return 0;
     const size_t xs_bytes = (size_t)M * K * sizeof(float);
-    if (few_rows(M, K)) {
+    // few rows of a very long K that do not fit shared memory together (the side-by-side down matrices of many experts): in halves,
+    // rather than on the tile kernels, which would run a handful of blocks over the whole K
+    const size_t mma_bytes = gemv_mma_smem_bytes(M, K);
+    // bf16 weights with K in whole 32-element chunks: the tensor-core form (a weight byte costs the same for 1 and for 8 rows; rows staged as bf16)
+    const bool mma_ok = M <= kRowGemvMaxRows && m.d.mode == TI_SEQ_BF16 && g_use_row_mma && K % 32 == 0 && K >= 256 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 &&
+                        mma_bytes <= g_smem_optin;
+    if (!fuse && M > 1 && M <= kRowGemvMaxRows && !mma_ok && !few_rows(M, K) && few_rows(1, K)) {
+        const int half = M / 2;
+        TRY(gemm(m, A, lda, W, C, ldc, half, N, K, epi, alpha));
+        return gemm(m, A + (size_t)half * lda, lda, W, C + (size_t)half * ldc, ldc, M - half, N, K, epi, alpha);
+    }
+    if (mma_ok || few_rows(M, K)) {
         const int warps = kRowGemvThreads / 32;
         // enough resident blocks to keep the memory system busy, few enough that staging the rows in every block stays small
         // beside the weight bytes: 2 blocks an SM (their registers allow no more) as far as their shared memory allows, columns looped inside
         const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, (200u << 10) / std::max<size_t>(xs_bytes, 1)));
         const int grid = std::max(1, std::min((N + warps - 1) / warps, g_num_sms * per_sm));
         const Fuse f = fuse ? *fuse : Fuse{};
-        // bf16 weights with K in whole 32-element chunks: the tensor-core form (a weight byte costs the same for 1 and for 8 rows)
-        const size_t mma_bytes = gemv_mma_smem_bytes(M, K);
-        if (m.d.mode == TI_SEQ_BF16 && g_use_row_mma && K % 32 == 0 && K >= 256 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 && mma_bytes <= g_smem_optin) {
+        if (mma_ok) {
             const int fit = (int)std::max<size_t>(1, std::min<size_t>(2, (200u << 10) / mma_bytes));
             const int blocks = std::max(1, std::min((N + kMmaCols - 1) / kMmaCols, g_num_sms * fit));
             cudaLaunchConfig_t cfg{};
@@ -832,7 +841,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         const size_t smem = ((size_t)kAttnWarps * s.vdim + 2 * kAttnWarps) * sizeof(float);
         const bool v_in_k = kp == vp && s.kv_heads == 1 && s.v_ld == s.dim && s.vdim <= s.dim;
         const size_t tsmem = attn_tiled_smem_bytes(s.dim, s.vdim, v_in_k);
-        const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && tsmem <= g_smem_optin && (s.v_ld % 4 == 0);
+        const bool tiled_ok = g_use_tiled_attn && n_tiles > 0 && s.dim % 4 == 0 && s.vdim % 4 == 0 && s.vdim <= 512 && tsmem <= g_smem_optin && (s.v_ld % 4 == 0);
         // bf16 mode, head sizes 64 / 128: the split-half tensor-core kernel (fp32-accurate); fp32 mode keeps true fp32 arithmetic
         const bool h3_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles128 > 0 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
                            (s.kv_heads * s.dim) % 4 == 0 && !s.sink && s.v_ld == 0;
@@ -882,7 +891,13 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         const bool attn = mixer == TI_SEQ_MIXER_ATTENTION;
         // decode steps (few rows) fuse the norm in front of the attention projections into the product's prologue
         const bool fuse_rows = few_rows(T, D) && !L.d.res_gate;
-        if (!(fuse_rows && attn)) {
+        // the mixers with ONE fused input projection (residual gate included) take the norm into that product's prologue as well
+        const bool fuse_front = few_rows(T, D) && (mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2 || mixer == TI_SEQ_MIXER_LATENT) && !L.rg1;
+        Fuse ff1;
+        ff1.norm_gain = L.norm1; ff1.eps = eps; ff1.gvec = gv;
+        const float* front_in = fuse_front ? m.x.p : m.h.p;
+        const Fuse* front_fuse = fuse_front ? &ff1 : nullptr;
+        if (!(fuse_rows && attn) && !fuse_front) {
             TRY(launch_dep(rmsnorm_kernel, dim3(T), dim3(nt), 0, (const float*)m.x.p, (const int*)nullptr, D, L.norm1, gv, eps, m.h.p));
             LAUNCHED();
         }
@@ -952,7 +967,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         } else if (mixer == TI_SEQ_MIXER_GLA || mixer == TI_SEQ_MIXER_HGRN2) {
             const bool gla = mixer == TI_SEQ_MIXER_GLA;
             const int H = L.d.heads, dk = L.d.dim, dv = L.d.vdim, C = H * dk, Cv = H * dv, nf = L.n_front;
-            TRY(gemm(m, m.h.p, D, L.front, m.proj.p, nf, T, nf, D));
+            TRY(gemm(m, front_in, D, L.front, m.proj.p, nf, T, nf, D, EPI_NONE, 1.f, front_fuse));
             LinScanArgs a{};
             a.q = m.proj.p + L.off_q; a.ldq = nf;
             a.v = m.proj.p + L.off_v; a.ldv = nf;
@@ -993,7 +1008,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             TRY(gemm(m, m.att.p, Cv, L.o, m.mo.p, D, T, D, Cv));
         } else {   // latent attention
             const int H = L.d.heads, d = L.d.dim, dr = L.d.rot_dims, dv = L.d.vdim, rank = L.d.kv_rank, kd = rank + dr, nf = L.n_front;
-            TRY(gemm(m, m.h.p, D, L.front, m.proj.p, nf, T, nf, D));
+            TRY(gemm(m, front_in, D, L.front, m.proj.p, nf, T, nf, D, EPI_NONE, 1.f, front_fuse));
             float* pool = R.kv_run >= 0 ? m.runs[R.kv_run].k_pool.p : R.k_pool.p;
             LatentShape ls{};
             ls.heads = H; ls.dim = d; ls.rot = dr; ls.rank = rank; ls.ld = nf; ls.off_q = L.off_q; ls.off_dkv = L.off_dkv; ls.eps = eps;
