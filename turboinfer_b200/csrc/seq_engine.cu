@@ -529,6 +529,7 @@ struct Fuse {
     int gvec = 0;
     float eps = 0.f;
     int glu_ff = 0, glu_act = 0;        // act(gate) * up behind a fused [gate | up] product: N is then the inner size
+    ExpertSkip nskip{}, kskip{};        // few rows over stacked expert matrices: column tiles / k chunks of experts no row chose are not read
 };
 bool few_rows(int M, int K) { return M <= kRowGemvMaxRows && (size_t)M * K * sizeof(float) <= g_smem_optin; }
 
@@ -542,10 +543,11 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
     // bf16 weights with K in whole 32-element chunks: the tensor-core form (a weight byte costs the same for 1 and for 8 rows; rows staged as bf16)
     const bool mma_ok = M <= kRowGemvMaxRows && m.d.mode == TI_SEQ_BF16 && g_use_row_mma && K % 32 == 0 && K >= 256 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 &&
                         mma_bytes <= g_smem_optin;
-    if (!fuse && M > 1 && M <= kRowGemvMaxRows && !mma_ok && !few_rows(M, K) && few_rows(1, K)) {
+    const bool plain = !fuse || (!fuse->norm_gain && !fuse->glu_ff);   // (a request to skip unused experts' rows is only a permission)
+    if (plain && M > 1 && M <= kRowGemvMaxRows && !mma_ok && !few_rows(M, K) && few_rows(1, K)) {
         const int half = M / 2;
-        TRY(gemm(m, A, lda, W, C, ldc, half, N, K, epi, alpha));
-        return gemm(m, A + (size_t)half * lda, lda, W, C + (size_t)half * ldc, ldc, M - half, N, K, epi, alpha);
+        TRY(gemm(m, A, lda, W, C, ldc, half, N, K, epi, alpha, fuse));
+        return gemm(m, A + (size_t)half * lda, lda, W, C + (size_t)half * ldc, ldc, M - half, N, K, epi, alpha, fuse);
     }
     if (mma_ok || few_rows(M, K)) {
         const int warps = kRowGemvThreads / 32;
@@ -569,10 +571,10 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
             cfg.numAttrs = g_use_pdl ? 1 : 0;
             if (f.glu_ff > 0)
                 CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<true>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
-                                      f.glu_act, f.gvec));
+                                      f.glu_act, f.gvec, f.nskip, f.kskip));
             else
                 CK(cudaLaunchKernelEx(&cfg, gemv_rows_mma_kernel<false>, A, lda, (const __nv_bfloat16*)W, C, ldc, M, N, K, epi, alpha, f.norm_gain, f.eps, f.glu_ff,
-                                      f.glu_act, f.gvec));
+                                      f.glu_act, f.gvec, f.nskip, f.kskip));
             LAUNCHED();
             return 0;
         }
@@ -595,7 +597,7 @@ int gemm(Model& m, const float* A, int lda, const void* W, float* C, int ldc, in
         LAUNCHED();
         return 0;
     }
-    if (fuse) return fail("internal: a fused product was asked for on the many-row path");
+    if (!plain) return fail("internal: a fused product was asked for on the many-row path");
     // prompt-sized products in bf16 mode: tcgen05 (TMA wants 16-byte row pitches and bases)
     if (m.d.mode == TI_SEQ_BF16 && g_use_tc && M > 32 && N >= 64 && K >= 64 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 && m.abf.p &&
         (size_t)M * K <= m.abf.n) {
@@ -1038,6 +1040,7 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 gate2_ld = L.n_ffront;
             }
             const float* idw = nullptr;
+            bool down_done = false;
             const int F = L.d.ff;
             if (L.d.ff_kind == TI_SEQ_FF_GLU) {
                 if (fuse_ff) {   // norm -> [gate | up] -> act(gate) * up in one launch
@@ -1055,23 +1058,43 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
                 LAUNCHED();
             } else {
                 const int nfw = L.n_ffront, Ex = L.d.experts;
-                TRY(gemm(m, m.h.p, D, L.ffront, m.proj.p, nfw, T, nfw, D));
                 RouteShape r{};
                 r.n_real = Ex; r.n_id = L.d.identity; r.top = L.d.top; r.groups = L.d.groups; r.keep = L.d.groups_keep;
                 float* wdense = m.route.p;
                 float* idw_buf = m.route.p + (size_t)T * std::max(Ex, 1);
-                const int rw = 4;
-                const size_t rsm = (size_t)rw * (2 * (Ex + L.d.identity) + 2 * L.d.groups) * sizeof(float);
-                TRY(launch_dep(moe_route_kernel, dim3((T + rw - 1) / rw), dim3(rw * 32), rsm, (const float*)m.proj.p, nfw, L.off_router, r, L.correction, T, wdense, idw_buf));
-                LAUNCHED();
+                const size_t rper = (size_t)(2 * (Ex + L.d.identity) + 2 * L.d.groups) * sizeof(float);
+                // few rows: [router | shared scale | residual gate] first, then the experts' rows with the ones nobody chose left out
+                const bool sparse = few_rows(T, D) && bf && Ex > 0 && L.off_up > 0 && T * rper <= 40 * 1024;
+                if (sparse) {
+                    int* used = reinterpret_cast<int*>(idw_buf + T);
+                    TRY(gemm(m, m.h.p, D, L.ffront, m.proj.p, nfw, T, L.off_up, D));
+                    TRY(launch_dep(moe_route_kernel, dim3(1), dim3(T * 32), T * rper, (const float*)m.proj.p, nfw, L.off_router, r, L.correction, T, wdense, idw_buf, used));
+                    LAUNCHED();
+                    Fuse f;
+                    f.nskip = ExpertSkip{used, 0, 2 * F, Ex};
+                    TRY(gemm(m, m.h.p, D, (const uint8_t*)L.ffront + (size_t)L.off_up * D * m.wsize, m.proj.p + L.off_up, nfw, T, nfw - L.off_up, D, EPI_NONE, 1.f, &f));
+                } else {
+                    TRY(gemm(m, m.h.p, D, L.ffront, m.proj.p, nfw, T, nfw, D));
+                    const int rw = 4;
+                    TRY(launch_dep(moe_route_kernel, dim3((T + rw - 1) / rw), dim3(rw * 32), rw * rper, (const float*)m.proj.p, nfw, L.off_router, r, L.correction, T, wdense, idw_buf,
+                                   (int*)nullptr));
+                    LAUNCHED();
+                }
                 if (L.ff_width > 0) {
                     TRY(launch_dep(moe_act_kernel, dim3(grid_for((size_t)T * L.ff_width)), dim3(256), 0, (const float*)m.proj.p, nfw, L.off_up, Ex, F, (const float*)wdense, L.off_sh,
                                    L.d.shared_ff, L.off_sg, m.act.p, T));
                     LAUNCHED();
                 }
+                if (sparse) {
+                    Fuse f;
+                    f.kskip = ExpertSkip{reinterpret_cast<const int*>(idw_buf + T), 0, F, Ex};
+                    TRY(gemm(m, m.act.p, L.ff_width, L.down, m.mo.p, D, T, D, L.ff_width, EPI_NONE, 1.f, &f));
+                    down_done = true;
+                }
                 if (L.d.identity > 0) idw = idw_buf;
             }
-            if (L.ff_width > 0) TRY(gemm(m, m.act.p, L.ff_width, L.down, m.mo.p, D, T, D, L.ff_width));
+            if (down_done) {}
+            else if (L.ff_width > 0) TRY(gemm(m, m.act.p, L.ff_width, L.down, m.mo.p, D, T, D, L.ff_width));
             else CK(cudaMemsetAsync(m.mo.p, 0, (size_t)T * D * sizeof(float), g_stream));
             TRY(post(L.norm2b, gv, nullptr, gate2, gate2_ld, L.rg2b, idw));
         } else {
@@ -1503,7 +1526,7 @@ int ti_seq_model_finalize(ti_seq_model_t h) {
                 for (const char* s : {"mlp.router", "mlp.shared.sg", "mlp.shared.gate", "mlp.shared.up", "mlp.shared.down", "rg2"}) release(p + s);
                 L.correction = F(p + "mlp.correction");
                 m.max_proj = std::max(m.max_proj, L.n_ffront);
-                m.max_route = std::max(m.max_route, std::max(E, 1) + 1);
+                m.max_route = std::max(m.max_route, 2 * std::max(E, 1) + 1);   // weights, identity weight, and (few rows) the experts' used flags
             }
             m.max_ff = std::max(m.max_ff, L.ff_width);
             if (L.d.res_gate) {

@@ -45,13 +45,14 @@ struct RouteShape {
 // `top` largest choice scores among them are picked (first index wins a tie); weights = s over the picked ones / (their sum + 1e-20).
 // wdense[t][e] = weight of real expert e or 0; idw[t] = sum of the weights of picked identity experts.
 // Shared memory per warp: s[n], choice[n], group score[groups], group kept[groups].
-__global__ void moe_route_kernel(const float* proj, int ld, int off, RouteShape r, const float* correction, int T, float* wdense, float* idw) {
+// used (optional; the grid is then ONE block that holds all rows): used[e] = 1 when some row picked real expert e, else 0.
+__global__ void moe_route_kernel(const float* proj, int ld, int off, RouteShape r, const float* correction, int T, float* wdense, float* idw, int* used) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     extern __shared__ float rsm[];
     const int n = r.n_real + r.n_id, per = 2 * n + 2 * r.groups;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= T) return;
+    if (t < T) {
     float* s = rsm + (size_t)warp * per;
     float* ch = s + n;
     float* gs = ch + n;
@@ -144,6 +145,15 @@ __global__ void moe_route_kernel(const float* proj, int ld, int off, RouteShape 
         }
     wi = warp_sum(wi);
     if (lane == 0) idw[t] = wi;
+    }
+    if (used) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < r.n_real; e += blockDim.x) {
+            int u = 0;
+            for (int x = 0; x < T; ++x) u |= wdense[(size_t)x * r.n_real + e] != 0.f;
+            used[e] = u;
+        }
+    }
 }
 
 // act[t][e * F + c] = wdense[t][e] * silu(gate_e[c]) * up_e[c] (0 without reading when the weight is 0), and behind the experts

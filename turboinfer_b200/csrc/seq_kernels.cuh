@@ -444,6 +444,21 @@ __global__ void __launch_bounds__(kRowGemvThreads) gemv_heads_rows_kernel(const 
 // order.  Needs K % 32 == 0 and 16-byte aligned weight rows.  Row stride in shared memory: K + 32 elements (rows of a quarter
 // warp fall into different banks).
 constexpr int kMmaCols = 16;
+// Routed experts on few rows: the stacked matrices hold every expert's rows, the step's tokens chose only some.  Output columns
+// (front product) or k (down product) in [first + e * group, first + (e + 1) * group) belong to expert e < count; a column tile or
+// k chunk whose experts were chosen by no row is not read (its outputs are never used / its activations are exactly zero).
+struct ExpertSkip {
+    const int* used;   // [count] 0 / 1; null: nothing is skipped
+    int first, group, count;
+};
+__device__ __forceinline__ bool expert_range_used(const ExpertSkip& s, int lo, int hi) {   // does [lo, hi] touch a used expert or leave the experts' range?
+    if (!s.used) return true;
+    if (lo < s.first) return true;
+    const int e0 = (lo - s.first) / s.group, e1 = (hi - s.first) / s.group;
+    for (int e = e0; e <= e1; ++e)
+        if (e >= s.count || s.used[e]) return true;
+    return false;
+}
 __host__ __device__ inline size_t gemv_mma_smem_bytes(int M, int K) { return (size_t)M * (K + 32) * 2 + 8 * 2 * 128 * sizeof(float); }
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -452,7 +467,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 template <bool GLU>
 __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int lda, const __nv_bfloat16* W, float* C, int ldc, int M, int N, int K, int epi,
-                                                           float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec) {
+                                                           float alpha, const float* norm_gain, float eps, int glu_ff, int glu_act, int gvec, ExpertSkip nskip,
+                                                           ExpertSkip kskip) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int Kp = K + 32;
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smraw);                       // [M][Kp]
@@ -522,18 +538,24 @@ __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int 
     }
     __syncthreads();
     constexpr int UNR = GLU ? 4 : 8;   // chunks whose weight loads are in flight together (16-byte loads a lane: 2 or 4 a chunk)
+    // when chunks may be skipped the warps take the chunks in turn (every warp gets its share of every expert) instead of one range each
+    const int cstep = kskip.used ? 8 : 1, c0 = kskip.used ? warp : c_begin, c1 = kskip.used ? NC : c_end;
     for (int n0 = blockIdx.x * kMmaCols; n0 < N; n0 += gridDim.x * kMmaCols) {
+        if (!expert_range_used(nskip, n0, min(n0 + kMmaCols, N) - 1)) continue;   // (uniform over the block)
         float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
         const __nv_bfloat16* w0 = W + (size_t)min(n0 + g, N - 1) * K + 8 * t;
         const __nv_bfloat16* w1 = W + (size_t)min(n0 + g + 8, N - 1) * K + 8 * t;
         const size_t up = (size_t)glu_ff * K;
         const __nv_bfloat16* xr = xs + (size_t)g * Kp + 8 * t;
-        for (int c = c_begin; c < c_end; c += UNR) {
+        for (int c = c0; c < c1; c += UNR * cstep) {
             uint4 ra[UNR], rb[UNR], ua[GLU ? UNR : 1], ub[GLU ? UNR : 1];
+            bool on[UNR];
 #pragma unroll
-            for (int q = 0; q < UNR; ++q)
-                if (c + q < c_end) {
-                    const int k = (c + q) * 32;
+            for (int q = 0; q < UNR; ++q) {
+                const int cc = c + q * cstep;
+                on[q] = cc < c1 && expert_range_used(kskip, cc * 32, cc * 32 + 31);
+                if (on[q]) {
+                    const int k = cc * 32;
                     ra[q] = *reinterpret_cast<const uint4*>(w0 + k);
                     rb[q] = *reinterpret_cast<const uint4*>(w1 + k);
                     if (GLU) {
@@ -541,11 +563,12 @@ __global__ void __launch_bounds__(256) gemv_rows_mma_kernel(const float* A, int 
                         ub[q] = *reinterpret_cast<const uint4*>(w1 + up + k);
                     }
                 }
+            }
 #pragma unroll
             for (int q = 0; q < UNR; ++q)
-                if (c + q < c_end) {
+                if (on[q]) {
                     uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                    if (g < M) x = *reinterpret_cast<const uint4*>(xr + (c + q) * 32);
+                    if (g < M) x = *reinterpret_cast<const uint4*>(xr + (c + q * cstep) * 32);
                     mma_bf16_16816(acc, ra[q].x, rb[q].x, ra[q].y, rb[q].y, x.x, x.y);
                     mma_bf16_16816(acc, ra[q].z, rb[q].z, ra[q].w, rb[q].w, x.z, x.w);
                     if (GLU) {
