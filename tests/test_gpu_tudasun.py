@@ -44,6 +44,7 @@ def weights(cfg, seed, dtype, **kw):
 MECHANISMS = {
     "gla": make_config([gla_layer()]),
     "gla_wide_keys_one_head": make_config([gla_layer(heads=1, dim=40, vdim=24, tau=3.0, rank=5), gla_layer(heads=2, dim=72, vdim=33, rank=1)], width=40, side=0),
+    "gla_many_value_columns": make_config([gla_layer(heads=2, dim=20, vdim=168, rank=3), hgrn2_layer(heads=1, dim=64, vdim=200)], width=40, side=0),
     "gla_state_in_shared_memory": make_config([gla_layer(heads=1, dim=136, vdim=40, rank=3)], width=64),
     "recurrence_128_key_channels": make_config([hgrn2_layer(heads=1, dim=128, vdim=40), gla_layer(heads=2, dim=128, vdim=96, rank=2)], width=64),
     "hgrn2": make_config([hgrn2_layer()]),
@@ -51,12 +52,13 @@ MECHANISMS = {
     "latent": make_config([latent_layer()]),
     "latent_odd_sizes": make_config([latent_layer(heads=3, dim=10, rot_dim=6, vdim=7, kv_rank=17, base=50.0)], width=36, eps=1e-3),
     "latent_no_rotation_part_of_two": make_config([latent_layer(heads=1, dim=16, rot_dim=2, vdim=16, kv_rank=16)]),
+    "latent_wide_cache_row": make_config([latent_layer(heads=2, dim=24, rot_dim=16, vdim=12, kv_rank=272)], width=40),
     "latent_shared_cache": make_config([latent_layer(mlp=dense(24)), gla_layer(), latent_layer(heads=4, dim=6, vdim=10, kv_from=0), latent_layer(kv_from=0)]),
     "dense_ff": make_config([hgrn2_layer(mlp=dense(56))]),
     "experts": make_config([gla_layer(mlp=moe())]),
     "experts_no_groups_no_identity_no_shared": make_config([hgrn2_layer(mlp=moe(experts=5, identity=0, top=3, count=0, shared=0))]),
     "experts_one_choice_every_group_kept": make_config([hgrn2_layer(mlp=moe(experts=3, identity=3, top=1, count=2, keep=2, ff=8, shared=8))], side=0),
-    "experts_many": make_config([gla_layer(mlp=moe(experts=37, identity=3, top=6, count=8, keep=3, ff=8, shared=0))]),
+    "experts_many": make_config([gla_layer(mlp=moe(experts=37, identity=3, top=9, count=8, keep=3, ff=8, shared=0))]),
     "no_side_input_no_cap": make_config([gla_layer(mlp=dense(32)), latent_layer()], side=0, softcap=0),
     "hybrid": make_config([gla_layer(mlp=dense(40)), latent_layer(mlp=moe()), hgrn2_layer(mlp=moe(experts=2, identity=1, top=2, count=3, keep=2)),
                            latent_layer(heads=3, kv_from=1), hgrn2_layer()], vocab=101, width=56, side=7),

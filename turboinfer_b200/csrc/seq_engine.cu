@@ -973,19 +973,17 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
             LinScanArgs a{};
             a.q = m.proj.p + L.off_q; a.ldq = nf;
             a.v = m.proj.p + L.off_v; a.ldv = nf;
-            if (gla) {   // decay = sigmoid(A2 (A1 h) + b)^(1 / tau)
+            if (gla) {   // decay = sigmoid(A2 (A1 h) + b)^(1 / tau): the scan turns the second product's output into decays as it stages them
                 TRY(gemm(m, m.proj.p + L.off_a1, nf, L.a2, m.aux.p, C, T, C, L.d.decay_rank));
-                TRY(launch_dep(gla_decay_kernel, dim3(grid_for((size_t)T * C)), dim3(256), 0, m.aux.p, L.a2b, 1.f / L.d.decay_tau, C, (size_t)T * C));
-                LAUNCHED();
                 a.k = m.proj.p + L.off_k; a.ldk = nf;
                 a.a = m.aux.p; a.lda = C;
                 a.qscale = 1.f / sqrtf((float)dk);
-            } else {     // q = silu(.), forget gate f = lower + (1 - lower) sigmoid(. + b) is the decay, 1 - f is written
-                TRY(launch_dep(hgrn2_gates_kernel, dim3(grid_for((size_t)T * C)), dim3(256), 0, m.proj.p, nf, L.off_q, L.off_k, L.fb, L.lower, C, T));
-                LAUNCHED();
+                a.gates = LIN_GATES_GLA; a.bias = L.a2b; a.lower = nullptr; a.inv_tau = 1.f / L.d.decay_tau;
+            } else {     // q = silu(.), forget gate f = lower + (1 - lower) sigmoid(. + b) is the decay, 1 - f is written (all inside the scan)
                 a.k = nullptr; a.ldk = 0;
                 a.a = m.proj.p + L.off_k; a.lda = nf;
                 a.qscale = 1.f;
+                a.gates = LIN_GATES_HGRN2; a.bias = L.fb; a.lower = L.lower; a.inv_tau = 1.f;
             }
             a.state = R.state.p; a.out = m.att.p; a.heads = H; a.dk = dk; a.dv = dv;
             const int threads = std::min(128, (dv + 31) / 32 * 32);

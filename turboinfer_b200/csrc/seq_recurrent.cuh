@@ -15,34 +15,27 @@
 namespace tib {
 namespace seq {
 
-// z [T][C] -> decay = exp(log_sigmoid(z + bias) / tau), in place; log_sigmoid(x) = min(x, 0) - log1p(exp(-|x|))
-__global__ void gla_decay_kernel(float* z, const float* bias, float inv_tau, int C, size_t n) {
-    pdl_launch_dependents();
-    pdl_wait_prior_grid();
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const float x = z[i] + bias[i % C];
-        const float ls = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
-        z[i] = expf(ls * inv_tau);
-    }
-}
-// in the fused projection rows: q <- silu(q), f <- lower + (1 - lower) * sigmoid(f + bias); C = heads * dk coordinates each
-__global__ void hgrn2_gates_kernel(float* proj, int ld, int off_q, int off_f, const float* bias, const float* lower, int C, int T) {
-    pdl_launch_dependents();
-    pdl_wait_prior_grid();
-    const size_t n = (size_t)T * C;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = i / C, c = i % C;
-        float* row = proj + t * ld;
-        const float q = row[off_q + c];
-        row[off_q + c] = q / (1.f + expf(-q));
-        const float lo = lower[c];
-        row[off_f + c] = lo + (1.f - lo) / (1.f + expf(-(row[off_f + c] + bias[c])));
+enum { LIN_GATES_GIVEN = 0, LIN_GATES_GLA = 1, LIN_GATES_HGRN2 = 2 };
+// What the scan does to its raw operands while it stages them (fp32):
+//   GIVEN  q and the decay are used as they are
+//   GLA    decay = exp(log_sigmoid(z + bias) / tau), log_sigmoid(x) = min(x, 0) - log1p(exp(-|x|))
+//   HGRN2  q = z_q * sigmoid(z_q), decay = lower + (1 - lower) * sigmoid(z + bias)
+__device__ __forceinline__ void lin_gates(int mode, float& q, float& dec, float bias, float lower, float inv_tau) {
+    if (mode == LIN_GATES_GLA) {
+        const float x = dec + bias;
+        dec = expf((fminf(x, 0.f) - log1pf(expf(-fabsf(x)))) * inv_tau);
+    } else if (mode == LIN_GATES_HGRN2) {
+        q = q / (1.f + expf(-q));
+        dec = lower + (1.f - lower) / (1.f + expf(-(dec + bias)));
     }
 }
 
 struct LinScanArgs {
     const float *q, *k, *a, *v;   // rows t, head hd: q / k / a at [t * ld + hd * dk + i], v at [t * ldv + hd * dv + j]; k == null: w = 1 - a
     int ldq, ldk, lda, ldv;
+    int gates;                    // LIN_GATES_*: how q and a become the query and the decay
+    const float *bias, *lower;    // [heads * dk] each (lower: HGRN2 only)
+    float inv_tau;
     float qscale;
     float* state;                 // [slots][heads][dk][dv]
     float* out;                   // [T][heads * dv]
@@ -81,8 +74,9 @@ __global__ void __launch_bounds__(128) linear_scan_kernel(LinScanArgs a, StepMet
         for (int x = threadIdx.x; x < nc * dk; x += blockDim.x) {
             const int c = x / dk, i = x % dk;
             const size_t t = (size_t)(tc + c);
-            const float dec = a.a[t * a.lda + (size_t)hd * dk + i];
-            stage[(c * 3 + 0) * dk + i] = a.q[t * a.ldq + (size_t)hd * dk + i] * a.qscale;
+            float dec = a.a[t * a.lda + (size_t)hd * dk + i], qv = a.q[t * a.ldq + (size_t)hd * dk + i];
+            if (a.gates != LIN_GATES_GIVEN) lin_gates(a.gates, qv, dec, a.bias[hd * dk + i], a.lower ? a.lower[hd * dk + i] : 0.f, a.inv_tau);
+            stage[(c * 3 + 0) * dk + i] = qv * a.qscale;
             stage[(c * 3 + 1) * dk + i] = a.k ? a.k[t * a.ldk + (size_t)hd * dk + i] : 1.f - dec;
             stage[(c * 3 + 2) * dk + i] = dec;
         }
@@ -154,6 +148,13 @@ __global__ void __launch_bounds__(32 * NW) linear_scan_split_kernel(LinScanArgs 
 #pragma unroll
     for (int i = 0; i < RP; ++i) S[i] = (own && !fresh) ? Sg[(size_t)(warp * RP + i) * dv + j] : 0.f;
     const int t0 = m.ent_row0[e], t1 = m.ent_row0[e + 1];
+    float gb[PER], gl[PER];   // the gates' per-channel constants of the channels this thread stages
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        const int i = (tid + NT * p) % DK;
+        gb[p] = a.gates != LIN_GATES_GIVEN ? a.bias[hd * DK + i] : 0.f;
+        gl[p] = a.lower ? a.lower[hd * DK + i] : 0.f;
+    }
     float nq[PER], nk[PER], na[PER], nv[VPER];
     auto fetch = [&](int tc) {
 #pragma unroll
@@ -187,9 +188,11 @@ __global__ void __launch_bounds__(32 * NW) linear_scan_split_kernel(LinScanArgs 
 #pragma unroll
         for (int p = 0; p < PER; ++p) {
             const int x = tid + NT * p, c = x / DK, i = x % DK;
-            buf[c][0][i] = nq[p] * a.qscale;
-            buf[c][1][i] = a.k ? nk[p] : 1.f - na[p];
-            buf[c][2][i] = na[p];
+            float qv = nq[p], dec = na[p];
+            if (a.gates != LIN_GATES_GIVEN) lin_gates(a.gates, qv, dec, gb[p], gl[p], a.inv_tau);
+            buf[c][0][i] = qv * a.qscale;
+            buf[c][1][i] = a.k ? nk[p] : 1.f - dec;
+            buf[c][2][i] = dec;
         }
 #pragma unroll
         for (int p = 0; p < VPER; ++p) {
