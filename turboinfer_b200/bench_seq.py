@@ -127,7 +127,13 @@ def measure_seq(size: str, dtype: str, n_prompt: int, n_new: int, batch: int, st
     launches = seq.launch_count() - launches0
     m.free()
     pre_ms, dec_ms = statistics.median(pre_dev), statistics.median(dec_dev)
-    return {"prefill_tokens_per_s": n_prompt / (pre_ms * 1e-3), "prefill_ms": pre_ms, "prefill_e2e_tokens_per_s": n_prompt / statistics.median(pre_wall),
+    # routed experts: a decode step reads only the experts its rows chose; with one row that is at most `top` of them a layer
+    idle = sum((L["mlp"]["router"]["experts"] - min(L["mlp"]["router"]["top"], L["mlp"]["router"]["experts"])) * 3.0 * L["mlp"]["expert"]["ff"] * cfg["width"] * 2.0
+               for L in cfg["layers"] if L.get("mlp") and L["mlp"].get("kind") == "moe")
+    extra = {}
+    if idle and batch == 1:
+        extra = {"weight_bytes_one_row": by["weights"] - idle, "decode_weight_GBps_one_row": (by["weights"] - idle) / (dec_ms * 1e-3) / 1e9}
+    return {**extra, "prefill_tokens_per_s": n_prompt / (pre_ms * 1e-3), "prefill_ms": pre_ms, "prefill_e2e_tokens_per_s": n_prompt / statistics.median(pre_wall),
             "decode_tokens_per_s": batch / (dec_ms * 1e-3), "decode_ms_per_step": dec_ms,
             "decode_e2e_tokens_per_s": batch / statistics.median(dec_wall), "batch": batch, "weight_bytes": by["weights"],
             "decode_weight_GBps": by["weights"] / (dec_ms * 1e-3) / 1e9, "gpu_launches": launches}
