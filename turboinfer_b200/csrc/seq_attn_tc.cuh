@@ -289,13 +289,17 @@ __global__ void attention_merge_kernel(const float* part, const float* qkvg, Ste
         gate = 1.f / (1.f + expf(-zg));
     }
     const float fin = attn_finish_factor(s, h, Mx, L) * gate;
+    // every split's factor in registers first, so that the loads of a coordinate's partials do not wait on one another
+    constexpr int kMaxSplits = 32;   // (a lane holds a split's statistics)
+    float fs[kMaxSplits];
+#pragma unroll
+    for (int z = 0; z < kMaxSplits; ++z) fs[z] = __shfl_sync(0xFFFFFFFFu, fz, z);
     for (int d0 = 0; d0 < s.vdim; d0 += 32) {
         const int d = d0 + lane;
         float acc = 0.f;
-        for (int z = 0; z < splits; ++z) {
-            const float f = __shfl_sync(0xFFFFFFFFu, fz, z);
-            if (d < s.vdim) acc = fmaf(p[(size_t)z * ps + 2 + d], f, acc);
-        }
+#pragma unroll
+        for (int z = 0; z < kMaxSplits; ++z)
+            if (z < splits && d < s.vdim) acc = fmaf(p[(size_t)z * ps + 2 + d], fs[z], acc);
         if (d < s.vdim) out[(size_t)t * (s.heads * s.vdim) + (size_t)h * s.vdim + d] = acc * fin;
     }
 }
