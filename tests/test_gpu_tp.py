@@ -23,7 +23,7 @@ def test_tp2_tokens_equal_single_gpu(engine):
     """fused: the persistent kernel with peer stores over NVLink, the partials exchanged point to point per column slice as tagged
     8-byte words the reader polls (default, "ll");
     fused-p2p: the same exchange with separate flags behind a system-scope release;
-    fused-barrier: a barrier across the GPUs + a reduce phase instead (round 1's default);
+    fused-barrier: a barrier across the GPUs + a reduce phase instead (the first exchange that was built);
     nccl: the per-op engine with ncclAllReduce after every row-parallel GEMV (the baseline of SURVEY.md 8e)."""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", {"fused": "29533", "fused-p2p": "29535", "fused-barrier": "29536", "nccl": "29534"}[engine],
