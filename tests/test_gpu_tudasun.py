@@ -104,6 +104,27 @@ def test_prefill_equals_token_by_token(dtype):
     check_logits(b, a, dtype)
 
 
+@pytest.mark.parametrize("rank,rot", [(256, 64), (128, 64), (128, 32)])
+def test_latent_prompts_on_the_tensor_cores(rank, rot):
+    """bf16 mode, cache rows of 256 + 64, 128 + 64 and 128 + 32: prompt portions of latent attention run on the split-half tensor-core kernel (tiles of
+    64 rows, key tiles = pages, both halves of the value columns), single tokens on the row kernels; a large sink on one head."""
+    cfg = make_config([latent_layer(heads=3, dim=32, rot_dim=rot, vdim=24, kv_rank=rank, mlp=dense(48)), latent_layer(heads=2, dim=16, rot_dim=rot, vdim=40, kv_rank=rank, kv_from=0)],
+                      width=64)
+    W = random_weights(cfg, seed=21)
+    W["l0.mix.sink"] = to_bf16_values(np.array([2.0, -1.0, 0.5], np.float32))
+    toks = tokens(330, cfg["vocab"], 21)
+    want, _ = PlainTudasun(cfg, W).run(toks)
+    m = build_engine(cfg, W, "bfloat16")
+    a = whole(m, toks)
+    b = run_schedule(m, {"a": toks}, [[("a", 130)], [("a", 70)], [("a", 9)], [("a", 100)]] + [[("a", 1)]] * 21)["a"]
+    m.free()
+    m = build_engine(cfg, W, "float32")
+    c = whole(m, toks)
+    m.free()
+    assert rel_err(a, want) < TOL["bfloat16"] and rel_err(b, want) < TOL["bfloat16"] and rel_err(c, want) < TOL["float32"]
+    assert rel_err(b, a) < 2e-2
+
+
 @pytest.mark.parametrize("sizes", [[2] * 40, [3, 61, 2, 64, 5, 65, 1, 63, 2], [64, 64, 64], [1, 127, 2, 2, 100], [129, 2, 33]])
 def test_portions(sizes):
     toks = tokens(sum(sizes), HYBRID["vocab"], 7)

@@ -847,9 +847,18 @@ int run_step(Model& m, int E, const int32_t* seqs, const int32_t* counts, const 
         // bf16 mode, head sizes 64 / 128: the split-half tensor-core kernel (fp32-accurate); fp32 mode keeps true fp32 arithmetic
         const bool h3_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles128 > 0 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
                            (s.kv_heads * s.dim) % 4 == 0 && !s.sink && s.v_ld == 0;
-        const int* rest = (tiled_ok || h3_ok) ? d_small : nullptr;
-        const int n_rest = (tiled_ok || h3_ok) ? n_small : T;
-        if (h3_ok) {
+        // bf16 mode, a shared key/value head with the values inside the key rows (latent attention), instantiated sizes: tensor cores
+        const bool lat_size = (s.dim == 320 && s.vdim == 256) || (s.dim == 192 && s.vdim == 128) || (s.dim == 160 && s.vdim == 128);
+        const bool lat_ok = g_use_tiled_attn && g_use_tc && bf && n_tiles > 0 && v_in_k && s.window == 0 && !s.out_gate && !s.qk_norm && lat_size;
+        const int* rest = (tiled_ok || h3_ok || lat_ok) ? d_small : nullptr;
+        const int n_rest = (tiled_ok || h3_ok || lat_ok) ? n_small : T;
+        if (lat_ok) {
+            const dim3 grid(n_tiles, s.heads);
+            if (s.dim == 320) latent_attention_h3_kernel<320, 256><<<grid, 256, latent_h3_smem_bytes<320>(), g_stream>>>(q, sm, s, d_tiles, kp, out);
+            else if (s.dim == 192) latent_attention_h3_kernel<192, 128><<<grid, 256, latent_h3_smem_bytes<192>(), g_stream>>>(q, sm, s, d_tiles, kp, out);
+            else latent_attention_h3_kernel<160, 128><<<grid, 256, latent_h3_smem_bytes<160>(), g_stream>>>(q, sm, s, d_tiles, kp, out);
+            LAUNCHED();
+        } else if (h3_ok) {
             const dim3 grid(n_tiles128, s.heads);
             if (s.dim == 64) window_attention_h3_kernel<64><<<grid, kTcThreads, attn_h3_smem_bytes<64>(), g_stream>>>(q, sm, s, d_tiles128, kp, vp, out);
             else window_attention_h3_kernel<128><<<grid, kTcThreads, attn_h3_smem_bytes<128>(), g_stream>>>(q, sm, s, d_tiles128, kp, vp, out);
@@ -1221,6 +1230,9 @@ int ti_seq_init(int device) {
     CK(cudaFuncSetAttribute(wkv_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(window_attention_tiled_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
     CK(cudaFuncSetAttribute(linear_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_smem_optin));
+    CK(cudaFuncSetAttribute(latent_attention_h3_kernel<320, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<320>()));
+    CK(cudaFuncSetAttribute(latent_attention_h3_kernel<192, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<192>()));
+    CK(cudaFuncSetAttribute(latent_attention_h3_kernel<160, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)latent_h3_smem_bytes<160>()));
     CK(cudaFuncSetAttribute(sample_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     CK(cudaFuncSetAttribute(sample_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024));
     g_device = device;
